@@ -1,0 +1,165 @@
+/*
+ * pilotann_b200.h -- C ABI of the B200 (sm_100a) GPU search stage.
+ *
+ * Plain pointers and sizes only; no torch / C++ types.  Every pointer is a
+ * DEVICE pointer on the current CUDA device unless its name starts with
+ * "host_".  `stream` is a cudaStream_t passed as void* (NULL = default stream).
+ * All calls are asynchronous on `stream` unless stated otherwise and return 0
+ * (PA_OK) or a negative error code; pa_last_error() gives the message of the
+ * last failure on the calling thread.  The library never falls back to the
+ * CPU: without a usable CUDA device every compute call fails with
+ * PA_ERR_CUDA.
+ *
+ * "Upstream" below = the PilotANN reference repository; paths are relative to
+ * its root.  The Python binding that mirrors the upstream pybind11 module over
+ * this ABI is pilotann_b200/extension.py.
+ */
+#ifndef PILOTANN_B200_H
+#define PILOTANN_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PA_OK 0
+#define PA_ERR_ARG (-1)        /* a shape / size / alignment the call rejects */
+#define PA_ERR_CUDA (-2)       /* a CUDA runtime call or a launch failed */
+#define PA_ERR_UNPACKABLE (-3) /* pa_pack_graph: input cannot be represented */
+#define PA_ERR_STATE (-4)      /* stage object used out of order */
+
+#define PA_BEAMS 4             /* beams per query, traverse_cuda.cu:13 */
+
+int pa_version(void);
+const char *pa_last_error(void);
+
+/* Heap capacity the traversal uses for a given ef_search (32/64/128/256), or
+ * -1 if ef_search is outside (0, 2048].  Upstream: traverse_cuda.cu:302-315. */
+int pa_heap_size_for(int ef_search);
+
+/* ---- traversal, upstream tensor layout --------------------------------
+ * Replaces `traverse_cuda` (extension/traverse_cuda.cu:249-315, declared in
+ * extension/entry.cpp:32-38): multi-beam search of a batch of queries over the
+ * sampled sub-graph in the reduced space.
+ *   output_I [batch,4,ef] int64, output_D [batch,4,ef] f32: per beam, worst ->
+ *     best; (-1,+inf) pads first when a beam holds fewer than ef results,
+ *     (-1,-inf) tail when ef > 256.
+ *   indptr [n_nodes+1], indices [*], mapping [n_nodes] int64 (CSR over global
+ *     ids, -1 padded rows; mapping = row of `storage` or -1)
+ *   storage [n_storage,d_model] f32, query [batch,d_model] f32
+ *   initial_I / initial_D [batch,n_initials]: entry ids and their reduced
+ *     squared distances.
+ *   stats: NULL, or int32 [batch,4] = rounds, expanded nodes, distance
+ *     evaluations, bloom bits set.
+ * Rejects (PA_ERR_ARG) what upstream rejects: n_neighbors % 32 != 0,
+ * 4*n_neighbors > 256, ef_search > 2048; and d_model % 4 != 0 or pointers not
+ * 16-byte aligned (upstream would fault on those). */
+int pa_traverse_csr(int64_t *output_I, float *output_D, const int64_t *indptr,
+                    const int64_t *indices, const int64_t *mapping,
+                    const float *storage, const float *query,
+                    const int64_t *initial_I, const float *initial_D,
+                    int64_t batch, int64_t n_nodes, int64_t n_storage,
+                    int d_model, int n_neighbors, int n_initials, int ef_search,
+                    int32_t *stats, void *stream);
+
+/* ---- packed device-resident index --------------------------------------
+ * Counterpart of the device copies `IndexStaged.to` prepares
+ * (pilot_ann/layers/staged.py:124-139), laid out for one dependent load per
+ * hop: packed_nbr [n_storage, n_neighbors] of int32 pairs {global id, storage
+ * row} indexed by storage row, and row_of [n_nodes] int32 (= mapping).
+ * Fails with PA_ERR_UNPACKABLE (after a stream synchronise) if a node with a
+ * non-empty adjacency row has no storage row, or an id does not fit int32.
+ * Synchronous. */
+int pa_pack_graph(int32_t *packed_nbr, int32_t *row_of, const int64_t *indptr,
+                  const int64_t *indices, const int64_t *mapping, int64_t n_nodes,
+                  int64_t n_storage, int n_neighbors, void *stream);
+
+/* Same search as pa_traverse_csr, same outputs bit for bit, over the packed
+ * index (the fast path used by the stage object and the Python layers). */
+int pa_traverse_packed(int64_t *output_I, float *output_D,
+                       const int32_t *packed_nbr, const int32_t *row_of,
+                       const float *storage, const float *query,
+                       const int64_t *initial_I, const float *initial_D,
+                       int64_t batch, int64_t n_nodes, int64_t n_storage,
+                       int d_model, int n_neighbors, int n_initials,
+                       int ef_search, int32_t *stats, void *stream);
+
+/* ---- entry routing (FES) -----------------------------------------------
+ * Replaces `routing_cuda` (extension/routing_cuda.cu:70-113, entry.cpp:59-62)
+ * and the id gather that follows it in IndexEntry.search
+ * (pilot_ann/layers/entry.py:81-88).
+ *   router [batch] int64: nearest router of each query (exact order; ties ->
+ *     lowest index)
+ *   leaf_D [batch,n_leaves] f32: squared distances to that router's leaves
+ *   leaf_I: NULL, or [batch,n_leaves] int64 = entry_nodes[router[b], :]
+ *   route_vectors [n_routers,d], entry_nodes [n_routers,n_leaves] int64,
+ *   entry_vectors [n_routers,n_leaves,d] f32.
+ * n_leaves % 32 == 0 as upstream (routing_cuda.cu:90); d % 4 == 0. */
+int pa_route(int64_t *router, float *leaf_D, int64_t *leaf_I, const float *query,
+             const float *route_vectors, const int64_t *entry_nodes,
+             const float *entry_vectors, int64_t batch, int d_model,
+             int n_routers, int n_leaves, void *stream);
+
+/* ---- query projection ---------------------------------------------------
+ * Replaces the CPU `query @ VT.T` of IndexStaged.search
+ * (pilot_ann/layers/staged.py:198): out[b, j] = sum_k query[b,k] * VT[j,k] for
+ * j < d_out.  query [batch,d_model], VT [>= d_out, d_model] row-major, out
+ * [batch, ld_out] with ld_out >= d_out. */
+int pa_project(float *out, const float *query, const float *VT, int64_t batch,
+               int d_model, int d_out, int64_t ld_out, void *stream);
+
+/* ---- search stage object -------------------------------------------------
+ * Replaces the GPU half of `pipeline` (extension/pipeline_cpu.cpp:32-145): its
+ * static stream pool (:67-75), the per-call device and pinned handoff buffers
+ * (:78-96) and the chunked launch + asynchronous copy-back loop (:120-140).
+ * One object per device, created once, reused for every batch. */
+typedef struct pa_stage pa_stage;
+
+typedef struct pa_stage_index {
+    const int32_t *packed_nbr;   /* pa_pack_graph output */
+    const int32_t *row_of;
+    const float *storage;        /* [n_storage, d_principle] */
+    const float *VT;             /* [d_model, d_model] or NULL (no projection) */
+    const float *route_vectors;  /* NULL for the 'random' entry method */
+    const int64_t *entry_nodes;  /* [n_routers, n_leaves] or [n_leaves] */
+    const float *entry_vectors;  /* [n_routers, n_leaves, d_p] or [n_leaves, d_p] */
+    int64_t n_nodes, n_storage;
+    int d_model, d_principle, n_neighbors, n_routers, n_leaves;
+} pa_stage_index;
+
+/* max_batch = largest batch a call will pass, max_ef = largest ef_search. */
+int pa_stage_create(pa_stage **out, const pa_stage_index *index, int64_t max_batch,
+                    int max_ef, int n_streams);
+void pa_stage_destroy(pa_stage *stage);
+
+/* One pass of the stage over a batch held in HOST memory:
+ *   host_query [batch, d_model] f32 (raw, unrotated when index.VT != NULL)
+ *   host_rotated: NULL, or [batch, d_model] f32 <- full rotated queries (what
+ *     the CPU refinement needs)
+ *   host_out_I [batch, 4*ef] int64, host_out_D [batch, 4*ef] f32 <- the
+ *     candidate handoff, rows in the layout `traverse_refine` consumes
+ *     (pipeline_cpu.cpp:90-95).
+ * The batch is cut into `chunk` queries (0 = one chunk); chunks alternate
+ * between the stage's streams so that copy-in, kernels and copy-back overlap.
+ * Blocks until the handoff is complete.  Host buffers should be pinned. */
+int pa_stage_search(pa_stage *stage, const float *host_query, float *host_rotated,
+                    int64_t *host_out_I, float *host_out_D, int64_t batch,
+                    int ef_search, int64_t chunk);
+
+/* Device-resident variant (inputs already in HBM, outputs stay there);
+ * asynchronous on the stage's first stream; dev_query is the raw query.
+ * dev_stats may be NULL. Returns after enqueueing. */
+int pa_stage_search_device(pa_stage *stage, const float *dev_query,
+                           int64_t *dev_out_I, float *dev_out_D, int64_t batch,
+                           int ef_search, int32_t *dev_stats);
+int pa_stage_synchronize(pa_stage *stage);
+/* cudaStream_t of the stage's first stream (for event timing by the caller). */
+void *pa_stage_stream(pa_stage *stage);
+/* Kernels launched by this library on behalf of the calling process. */
+int64_t pa_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PILOTANN_B200_H */

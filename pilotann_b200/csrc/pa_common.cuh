@@ -1,0 +1,138 @@
+// Shared declarations of the sm_100a search-stage library: error plumbing,
+// the bloom hash and the three heap primitives whose exact semantics (element
+// layout included) decide which candidates a query keeps.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <math_constants.h>
+#include <stdint.h>
+
+#include "pilotann_b200.h"
+
+namespace pa {
+
+// ---- host-side error plumbing (api.cu) -----------------------------------
+int fail(int code, const char *fmt, ...);
+int cuda_fail(cudaError_t err, const char *what);
+void count_launch(int n = 1);
+
+#define PA_CUDA_TRY(expr)                                         \
+    do {                                                          \
+        cudaError_t err__ = (expr);                               \
+        if (err__ != cudaSuccess) return pa::cuda_fail(err__, #expr); \
+    } while (0)
+
+#define PA_REQUIRE(cond, ...)                                     \
+    do {                                                          \
+        if (!(cond)) return pa::fail(PA_ERR_ARG, __VA_ARGS__);    \
+    } while (0)
+
+// ---- launchers shared between translation units (used by stage.cu) -------
+int traverse_packed_launch(int64_t *output_I, float *output_D, const int32_t *packed_nbr,
+                           const int32_t *row_of, const float *storage, const float *query,
+                           int64_t ldq, const int64_t *initial_I, const float *initial_D,
+                           int64_t batch, int64_t n_nodes, int64_t n_storage, int d_model,
+                           int n_neighbors, int n_initials, int ef_search, int32_t *stats,
+                           cudaStream_t stream);
+int route_launch(int64_t *router, float *leaf_D, int64_t *leaf_I, const float *query,
+                 int64_t ldq, const float *route_vectors, const int64_t *entry_nodes,
+                 const float *entry_vectors, int64_t batch, int d, int n_routers, int n_leaves,
+                 cudaStream_t stream);
+int project_launch(float *out, const float *query, const float *VT, int64_t batch, int d,
+                   int d_out, int64_t ld_out, cudaStream_t stream);
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// ---- constants with search semantics (upstream traverse_cuda.cu:7-15) ----
+constexpr int kBeams = PA_BEAMS;        // BEAM_WIDTH
+constexpr int kTeam = 8;                // TEAM_SIZE: lanes per distance
+constexpr int kTeamsPerWarp = 4;        // N_WORKERS
+constexpr int kMaxSlots = 256;          // BUFFER_SIZE
+constexpr uint32_t kBloomBits = 32768;  // BITMASK_SIZE
+constexpr int kBloomWords = kBloomBits / 32;
+constexpr int kFnvSteps = 4;            // FNV_STEP
+constexpr uint32_t kFnvPrime = 0x01000193u;
+constexpr uint32_t kFnvOffset = 0x811c9dc5u;
+constexpr int kEmptyRowTag = -2;       // first pair of a packed row without adjacency
+
+// upstream bloom.cuh:9-16: the whole shifted word is xor-ed in at every step
+__host__ __device__ __forceinline__ uint32_t fnv1a_32(uint32_t x, uint32_t h) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        h ^= x >> (8 * i);
+        h *= kFnvPrime;
+    }
+    return h;
+}
+
+// ---- heaps (upstream heapq.cuh:13-87) ---------------------------------------
+// Binary min-heaps over parallel key / value arrays.  V is whatever rides with
+// the key (an id, or an id + row pair).
+
+template <typename V>
+__device__ __forceinline__ void sift_root_down(float *keys, V *vals, int hsize) {
+    // heapq.cuh:13-29
+    int cursor = 0;
+    float ck = keys[0];
+    V cv = vals[0];
+    for (int child = 1; child < hsize; child = 2 * cursor + 1) {
+        int right = child + 1;
+        float k = keys[child];
+        if (right < hsize) {
+            float kr = keys[right];
+            if (kr < k) { child = right; k = kr; }
+        }
+        if (ck <= k) break;
+        keys[cursor] = k;
+        vals[cursor] = vals[child];
+        cursor = child;
+    }
+    keys[cursor] = ck;
+    vals[cursor] = cv;
+}
+
+template <typename V>
+__device__ __forceinline__ void heap_pop(float *keys, V *vals, int hsize, V empty,
+                                         float &out_key, V &out_val) {
+    // heapq.cuh:38-45
+    out_key = keys[0];
+    out_val = vals[0];
+    keys[0] = CUDART_INF_F;
+    vals[0] = empty;
+    sift_root_down(keys, vals, hsize);
+}
+
+template <typename V>
+__device__ __forceinline__ void heap_replace(float *keys, V *vals, int hsize, float k, V v) {
+    // heapq.cuh:47-77: walk to a leaf along the larger child (right only if
+    // strictly larger), give up if the new key is not smaller, else overwrite
+    // that leaf and sift up while the parent is strictly larger
+    int cursor = 0;
+    for (int child = 1; child < hsize; child = 2 * cursor + 1) {
+        int right = child + 1;
+        if (right < hsize && keys[right] > keys[child]) child = right;
+        cursor = child;
+    }
+    if (k >= keys[cursor]) return;
+    while (cursor > 0) {
+        int parent = (cursor - 1) >> 1;
+        float pk = keys[parent];
+        if (pk <= k) break;
+        keys[cursor] = pk;
+        vals[cursor] = vals[parent];
+        cursor = parent;
+    }
+    keys[cursor] = k;
+    vals[cursor] = v;
+}
+
+template <typename V>
+__device__ __forceinline__ void heap_pushpop(float *keys, V *vals, int hsize, float k, V v) {
+    // heapq.cuh:79-87
+    if (k <= keys[0]) return;
+    keys[0] = k;
+    vals[0] = v;
+    sift_root_down(keys, vals, hsize);
+}
+
+}  // namespace pa

@@ -1,0 +1,83 @@
+// Builds the packed device-resident index from upstream's CSR tensors: the
+// counterpart of the device copies prepared by IndexStaged.to
+// (pilot_ann/layers/staged.py:124-139).  One warp per node.
+#include "pa_common.cuh"
+
+namespace pa {
+
+__global__ void pack_fill_kernel(int2 *nbr, int64_t n_pairs, int n_nb) {
+    int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (i < n_pairs) nbr[i] = make_int2((i % n_nb) == 0 ? kEmptyRowTag : -1, -1);
+}
+
+__global__ void pack_rows_kernel(int2 *__restrict__ nbr, int32_t *__restrict__ row_of,
+                                 const int64_t *__restrict__ indptr,
+                                 const int64_t *__restrict__ indices,
+                                 const int64_t *__restrict__ mapping, int64_t n_nodes,
+                                 int64_t n_storage, int n_nb, int *__restrict__ error) {
+    const int lane = threadIdx.x & 31;
+    const int64_t u = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5;
+    if (u >= n_nodes) return;
+    const int64_t row = mapping[u];
+    const int64_t lo = indptr[u], hi = indptr[u + 1];
+    if (lane == 0) row_of[u] = row < 0 ? -1 : static_cast<int32_t>(row);
+    if (row >= n_storage || row > 0x7ffffffe) { if (lane == 0) atomicExch(error, 2); return; }
+    if (row < 0) {
+        // a node without a vector row cannot carry an adjacency row here
+        if (hi != lo && lane == 0) atomicExch(error, 1);
+        return;
+    }
+    const int64_t len = min(hi - lo, static_cast<int64_t>(n_nb));
+    if (len <= 0) return;  // keeps the "empty row" tag written by the fill pass
+    for (int i = lane; i < n_nb; i += 32) {
+        int2 e = make_int2(-1, -1);
+        if (i < len) {
+            int64_t v = indices[lo + i];
+            if (v >= n_nodes) { atomicExch(error, 2); v = -1; }
+            if (v >= 0) {
+                int64_t r = mapping[v];
+                e = make_int2(static_cast<int32_t>(v), r < 0 ? -1 : static_cast<int32_t>(r));
+            }
+        }
+        nbr[row * n_nb + i] = e;
+    }
+}
+
+}  // namespace pa
+
+extern "C" int pa_pack_graph(int32_t *packed_nbr, int32_t *row_of, const int64_t *indptr,
+                             const int64_t *indices, const int64_t *mapping, int64_t n_nodes,
+                             int64_t n_storage, int n_neighbors, void *stream_) {
+    using namespace pa;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    PA_REQUIRE(n_neighbors > 0 && n_neighbors % 32 == 0, "n_neighbors must be a multiple of 32");
+    PA_REQUIRE(n_nodes >= 0 && n_nodes < 0x7fffffff && n_storage >= 0 && n_storage < 0x7fffffff,
+               "ids must fit int32");
+    PA_REQUIRE(packed_nbr && row_of && indptr && indices && mapping, "null pointer");
+    PA_REQUIRE((reinterpret_cast<uintptr_t>(packed_nbr) & 7u) == 0, "packed_nbr must be 8-byte aligned");
+    int *error = nullptr;
+    PA_CUDA_TRY(cudaMallocAsync(&error, sizeof(int), stream));
+    PA_CUDA_TRY(cudaMemsetAsync(error, 0, sizeof(int), stream));
+    const int64_t n_pairs = n_storage * n_neighbors;
+    if (n_pairs > 0) {
+        pack_fill_kernel<<<static_cast<unsigned>((n_pairs + 255) / 256), 256, 0, stream>>>(
+            reinterpret_cast<int2 *>(packed_nbr), n_pairs, n_neighbors);
+        count_launch();
+    }
+    if (n_nodes > 0) {
+        const int64_t threads = n_nodes * 32;
+        pack_rows_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, stream>>>(
+            reinterpret_cast<int2 *>(packed_nbr), row_of, indptr, indices, mapping, n_nodes,
+            n_storage, n_neighbors, error);
+        count_launch();
+    }
+    PA_CUDA_TRY(cudaGetLastError());
+    int host_error = 0;
+    PA_CUDA_TRY(cudaMemcpyAsync(&host_error, error, sizeof(int), cudaMemcpyDeviceToHost, stream));
+    PA_CUDA_TRY(cudaStreamSynchronize(stream));
+    PA_CUDA_TRY(cudaFreeAsync(error, stream));
+    if (host_error == 1)
+        return fail(PA_ERR_UNPACKABLE, "a node with neighbours has no storage row (mapping < 0)");
+    if (host_error == 2) return fail(PA_ERR_UNPACKABLE, "an id or storage row is out of range");
+    return PA_OK;
+}

@@ -1,0 +1,179 @@
+"""Python mirror of the upstream pybind11 module ``pilot_ann.extension`` for the
+GPU search stage (``extension/entry.cpp:65-86``): same function names, argument
+order and error behaviour (``RuntimeError``), implemented as ctypes calls into
+the C-ABI library.  Hot names: ``traverse_cuda``, ``routing_cuda``; plus the
+entry points that have no upstream counterpart because upstream keeps its
+tensors in CSR form (``pack_graph``, ``traverse_packed``, ``project``).
+
+Tensors are checked exactly as ``CHECK_CUDA`` does (``extension/inc/common.h:
+23-29``): CUDA device, rank, dtype, contiguity.  Work is enqueued on the
+current torch CUDA stream of the tensors' device, like upstream
+(``traverse_cuda.cu:284``); unlike upstream a device guard is applied.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _C
+
+BEAM_WIDTH = 4
+
+
+def _check_cuda(name: str, x: torch.Tensor, dim: int, dtype: torch.dtype) -> None:
+    if not isinstance(x, torch.Tensor) or not x.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor")
+    if x.dim() != dim:
+        raise RuntimeError(f"{name} must be of dim {dim}")
+    if x.dtype != dtype:
+        raise RuntimeError(f"{name} must be type of {dtype}")
+    if not x.is_contiguous():
+        raise RuntimeError(f"{name} custom kernel requires contiguous tensor")
+
+
+def _require(cond: bool, what: str) -> None:
+    if not cond:
+        raise RuntimeError(f"Expected {what} to be true, but got false.")
+
+
+def _stream(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _traverse_checks(output_I, output_D, storage, query, initial_I, initial_D, n_neighbors):
+    _check_cuda("storage", storage, 2, torch.float32)
+    _check_cuda("query", query, 2, torch.float32)
+    _check_cuda("initial_I", initial_I, 2, torch.int64)
+    _check_cuda("initial_D", initial_D, 2, torch.float32)
+    _check_cuda("output_I", output_I, 3, torch.int64)
+    _check_cuda("output_D", output_D, 3, torch.float32)
+    batch, d_model = query.shape
+    _require(storage.size(-1) == d_model, "storage.size(-1) == d_model")
+    _require(output_I.size(0) == batch, "output_I.size(0) == batch_size")
+    _require(output_I.size(1) == BEAM_WIDTH, "output_I.size(1) == BEAM_WIDTH")
+    _require(initial_I.size(0) == batch, "initial_I.size(0) == batch_size")
+    _require(output_I.shape == output_D.shape, "output_I.sizes() == output_D.sizes()")
+    _require(initial_I.shape == initial_D.shape, "initial_I.sizes() == initial_D.sizes()")
+    _require(BEAM_WIDTH * n_neighbors <= 256, "BEAM_WIDTH * n_neighbors <= BUFFER_SIZE")
+    _require(n_neighbors % 32 == 0, "n_neighbors % WARP_SIZE == 0")
+
+
+def traverse_cuda(output_I, output_D, indptr, indices, mapping, storage, query,
+                  initial_I, initial_D, n_neighbors: int, stats=None) -> None:
+    """``extension.traverse_cuda`` (``extension/traverse_cuda.cu:249-315``)."""
+    _check_cuda("indptr", indptr, 1, torch.int64)
+    _check_cuda("indices", indices, 1, torch.int64)
+    _check_cuda("mapping", mapping, 1, torch.int64)
+    _traverse_checks(output_I, output_D, storage, query, initial_I, initial_D, n_neighbors)
+    n_nodes = indptr.size(0) - 1
+    _require(mapping.size(0) == n_nodes, "mapping.size(0) == n_nodes")
+    if stats is not None:
+        _check_cuda("stats", stats, 2, torch.int32)
+    with torch.cuda.device(query.device):
+        _C.check(_C.lib().pa_traverse_csr(
+            output_I.data_ptr(), output_D.data_ptr(), indptr.data_ptr(), indices.data_ptr(),
+            mapping.data_ptr(), storage.data_ptr(), query.data_ptr(), initial_I.data_ptr(),
+            initial_D.data_ptr(), query.size(0), n_nodes, storage.size(0), query.size(1),
+            n_neighbors, initial_I.size(1), output_I.size(2),
+            0 if stats is None else stats.data_ptr(), _stream(query.device)))
+
+
+def pack_graph(indptr, indices, mapping, n_storage: int, n_neighbors: int):
+    """Packed device index from upstream's CSR tensors.  Returns
+    ``(packed_nbr int32 [n_storage, n_neighbors, 2], row_of int32 [n_nodes])``."""
+    _check_cuda("indptr", indptr, 1, torch.int64)
+    _check_cuda("indices", indices, 1, torch.int64)
+    _check_cuda("mapping", mapping, 1, torch.int64)
+    n_nodes = indptr.size(0) - 1
+    _require(mapping.size(0) == n_nodes, "mapping.size(0) == n_nodes")
+    dev = indptr.device
+    packed = torch.empty(n_storage, n_neighbors, 2, dtype=torch.int32, device=dev)
+    row_of = torch.empty(n_nodes, dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        _C.check(_C.lib().pa_pack_graph(
+            packed.data_ptr(), row_of.data_ptr(), indptr.data_ptr(), indices.data_ptr(),
+            mapping.data_ptr(), n_nodes, n_storage, n_neighbors, _stream(dev)))
+    return packed, row_of
+
+
+def traverse_packed(output_I, output_D, packed_nbr, row_of, storage, query, initial_I,
+                    initial_D, n_neighbors: int, stats=None) -> None:
+    """Same search as ``traverse_cuda`` over the packed index."""
+    _check_cuda("packed_nbr", packed_nbr, 3, torch.int32)
+    _check_cuda("row_of", row_of, 1, torch.int32)
+    _traverse_checks(output_I, output_D, storage, query, initial_I, initial_D, n_neighbors)
+    _require(packed_nbr.size(0) == storage.size(0), "packed_nbr.size(0) == n_storage")
+    _require(packed_nbr.size(1) == n_neighbors, "packed_nbr.size(1) == n_neighbors")
+    if stats is not None:
+        _check_cuda("stats", stats, 2, torch.int32)
+    with torch.cuda.device(query.device):
+        _C.check(_C.lib().pa_traverse_packed(
+            output_I.data_ptr(), output_D.data_ptr(), packed_nbr.data_ptr(), row_of.data_ptr(),
+            storage.data_ptr(), query.data_ptr(), initial_I.data_ptr(), initial_D.data_ptr(),
+            query.size(0), row_of.size(0), storage.size(0), query.size(1), n_neighbors,
+            initial_I.size(1), output_I.size(2), 0 if stats is None else stats.data_ptr(),
+            _stream(query.device)))
+
+
+def routing_cuda(query, route_vectors, entry_nodes, entry_vectors, with_ids: bool = False):
+    """``extension.routing_cuda`` (``extension/routing_cuda.cu:70-113``): returns
+    ``[router int64 [B], distances f32 [B, n_leaves]]`` (+ the gathered leaf ids
+    ``[B, n_leaves]`` when ``with_ids``)."""
+    _check_cuda("query", query, 2, torch.float32)
+    _check_cuda("route_vectors", route_vectors, 2, torch.float32)
+    _check_cuda("entry_vectors", entry_vectors, 3, torch.float32)
+    _check_cuda("entry_nodes", entry_nodes, 2, torch.int64)
+    batch, d_model = query.shape
+    n_leaves = entry_nodes.size(-1)
+    n_routers = route_vectors.size(0)
+    _require(route_vectors.size(-1) == d_model, "route_vectors.size(-1) == d_model")
+    _require(entry_vectors.size(-1) == d_model, "entry_vectors.size(-1) == d_model")
+    _require(entry_vectors.size(0) == n_routers, "entry_vectors.size(0) == n_routers")
+    _require(entry_vectors.size(1) == n_leaves, "entry_vectors.size(1) == n_leaves")
+    _require(n_leaves % 32 == 0, "n_leaves % BLOCK_SIZE == 0")
+    router = torch.empty(batch, dtype=torch.int64, device=query.device)
+    distances = torch.empty(batch, n_leaves, dtype=torch.float32, device=query.device)
+    ids = torch.empty(batch, n_leaves, dtype=torch.int64, device=query.device) if with_ids else None
+    with torch.cuda.device(query.device):
+        _C.check(_C.lib().pa_route(
+            router.data_ptr(), distances.data_ptr(), 0 if ids is None else ids.data_ptr(),
+            query.data_ptr(), route_vectors.data_ptr(), entry_nodes.data_ptr(),
+            entry_vectors.data_ptr(), batch, d_model, n_routers, n_leaves,
+            _stream(query.device)))
+    return [router, distances, ids] if with_ids else [router, distances]
+
+
+def entry_distances(query, entry_vectors):
+    """Squared distances from every query to one shared list of entry vectors
+    ``[n, d]`` (the 'random' entry method, ``pilot_ann/layers/entry.py:70-77``)."""
+    _check_cuda("query", query, 2, torch.float32)
+    _check_cuda("entry_vectors", entry_vectors, 2, torch.float32)
+    batch, d_model = query.shape
+    n = entry_vectors.size(0)
+    _require(entry_vectors.size(1) == d_model, "entry_vectors.size(-1) == d_model")
+    _require(n % 32 == 0, "n_entries % 32 == 0")
+    distances = torch.empty(batch, n, dtype=torch.float32, device=query.device)
+    with torch.cuda.device(query.device):
+        _C.check(_C.lib().pa_route(0, distances.data_ptr(), 0, query.data_ptr(), 0, 0,
+                                   entry_vectors.data_ptr(), batch, d_model, 1, n,
+                                   _stream(query.device)))
+    return distances
+
+
+def project(query, VT, d_out: int | None = None):
+    """``query @ VT.T`` on the GPU (``pilot_ann/layers/staged.py:198`` runs it on
+    the CPU); first ``d_out`` output columns."""
+    _check_cuda("query", query, 2, torch.float32)
+    _check_cuda("VT", VT, 2, torch.float32)
+    _require(VT.size(1) == query.size(1), "VT.size(1) == d_model")
+    d_out = VT.size(0) if d_out is None else d_out
+    _require(0 <= d_out <= VT.size(0), "d_out <= VT.size(0)")
+    out = torch.empty(query.size(0), d_out, dtype=torch.float32, device=query.device)
+    with torch.cuda.device(query.device):
+        _C.check(_C.lib().pa_project(out.data_ptr(), query.data_ptr(), VT.data_ptr(),
+                                     query.size(0), query.size(1), d_out, d_out,
+                                     _stream(query.device)))
+    return out
+
+
+def launch_count() -> int:
+    return int(_C.lib().pa_launch_count())
