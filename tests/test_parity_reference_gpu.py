@@ -1,0 +1,123 @@
+"""Side-by-side parity with the UPSTREAM CUDA kernels (compiled in place into
+oracle/_ref): identical graph, projection, entries and queries go to both.
+
+Gates: router ids and leaf ids bit-exact; reduced-space distances within 1e-5
+relative; recall@k within +-0.002; final top-k ids identical for at least
+99.5 % of queries -- or, where the upstream kernel does not reproduce ITSELF at
+that level, for at least as many queries as two runs of the upstream kernel on
+the same inputs agree on (plus a small margin).  The upstream traversal kernel
+is not deterministic: its warps race on the bloom filter and the filter is
+cleared without a barrier before the entries are inserted, so nodes get visited
+twice or not at all depending on timing; the test measures that run-to-run
+mismatch first.  The deterministic, bit-exact comparison is the one against the
+CPU oracle (test_traverse_parity.py), which fixes one legal interleaving."""
+import pytest
+import torch
+
+from helpers import make_problem, to_cuda, topk_ids
+
+pytestmark = pytest.mark.gpu
+
+
+def _ours(c, ef, n_nb, packed):
+    from pilotann_b200 import extension
+    B = c["query"].size(0)
+    oI = torch.empty(B, 4, ef, dtype=torch.int64, device="cuda")
+    oD = torch.empty(B, 4, ef, device="cuda")
+    if packed:
+        nbr, row_of = extension.pack_graph(c["indptr"], c["indices"], c["mapping"],
+                                           c["storage"].size(0), n_nb)
+        extension.traverse_packed(oI, oD, nbr, row_of, c["storage"], c["query"],
+                                  c["initial_I"], c["initial_D"], n_nb)
+    else:
+        extension.traverse_cuda(oI, oD, c["indptr"], c["indices"], c["mapping"], c["storage"],
+                                c["query"], c["initial_I"], c["initial_D"], n_nb)
+    torch.cuda.synchronize()
+    return oI.cpu(), oD.cpu()
+
+
+def _theirs(ref_ext, c, ef, n_nb):
+    B = c["query"].size(0)
+    oI = torch.empty(B, 4, ef, dtype=torch.int64, device="cuda")
+    oD = torch.empty(B, 4, ef, device="cuda")
+    ref_ext.traverse_cuda(oI, oD, c["indptr"], c["indices"], c["mapping"], c["storage"],
+                          c["query"], c["initial_I"], c["initial_D"], n_nb)
+    torch.cuda.synchronize()
+    return oI.cpu(), oD.cpu()
+
+
+def _recall(top, truth):
+    hit = sum(len(set(a) & set(b)) for a, b in zip(top, truth))
+    return hit / sum(len(b) for b in truth)
+
+
+@pytest.mark.parametrize("law,d,ratio,ef", [("fuzz", 64, 1.0, 64), ("powerlaw", 128, 0.25, 32),
+                                            ("mixture", 64, 0.25, 32), ("powerlaw", 128, 0.25, 128)])
+def test_traversal_vs_upstream_kernel(ref_ext, law, d, ratio, ef):
+    k = 10
+    p = make_problem(n=20000, d=d, ratio=ratio, batch=512, n_init=64, seed=21, law=law,
+                     build_device="cuda")
+    c = to_cuda(p)
+    theirs = _theirs(ref_ext, c, ef, 32)
+    theirs_again = _theirs(ref_ext, c, ef, 32)
+    t_top = topk_ids(*theirs, k)
+    jitter = sum(a != b for a, b in zip(t_top, topk_ids(*theirs_again, k))) / len(t_top)
+    truth = p["nodelist"][__import__("pilotann_b200").utils.ground_truth(
+        p["query"], p["full"][p["nodelist"]], k)].tolist()
+    for packed in (False, True):
+        ours = _ours(c, ef, 32, packed)
+        o_top = topk_ids(*ours, k)
+        same = sum(a == b for a, b in zip(o_top, t_top)) / len(t_top)
+        print(f"{law} d={d} ef={ef} packed={packed}: identical top-{k} {same:.4f} "
+              f"(upstream run-to-run mismatch {jitter:.4f})")
+        assert 1.0 - same <= max(0.005, 1.25 * jitter + 0.01)
+        # a query whose top-k differs typically differs in about one of its k ids, so
+        # upstream's own run-to-run mismatch moves its recall by ~jitter / k
+        assert abs(_recall(o_top, truth) - _recall(t_top, truth)) <= 0.002 + jitter / k
+        # distances of ids both sides report, within 1e-5 relative
+        for b in range(0, len(t_top), 17):
+            mine = dict(zip(ours[0][b].flatten().tolist(), ours[1][b].flatten().tolist()))
+            for i, dist in zip(theirs[0][b].flatten().tolist(), theirs[1][b].flatten().tolist()):
+                if i >= 0 and i in mine:
+                    assert abs(mine[i] - dist) <= 1e-5 * abs(dist)
+
+
+def test_routing_vs_upstream_kernel(ref_ext):
+    from pilotann_b200 import extension
+    g = torch.Generator().manual_seed(2)
+    n, d = 20000, 128
+    x = torch.nn.functional.normalize(torch.randn(n, d, generator=g), dim=-1)
+    q = torch.nn.functional.normalize(torch.randn(777, d, generator=g), dim=-1).cuda()
+    for n_r, n_l in ((16, 32), (64, 64)):
+        rv = x[torch.randint(n, (n_r,), generator=g)].contiguous().cuda()
+        en = torch.randint(n, (n_r, n_l), generator=g).cuda()
+        ev = x[en.cpu()].contiguous().cuda()
+        t_router, t_dist = ref_ext.routing_cuda(q, rv, en, ev)
+        o_router, o_dist, o_ids = extension.routing_cuda(q, rv, en, ev, with_ids=True)
+        torch.cuda.synchronize()
+        assert torch.equal(o_router, t_router)
+        assert torch.equal(o_ids, torch.index_select(en, 0, t_router))   # entry.py:86-88
+        assert torch.allclose(o_dist, t_dist, rtol=1e-5, atol=0.0)
+
+
+def test_golden_gpu_fixtures():
+    """Outputs of the upstream kernels recorded on a B200
+    (tests/golden/make_golden.py --gpu), replayed without the upstream module."""
+    from pathlib import Path
+    from pilotann_b200 import extension
+    gdir = Path(__file__).parent / "golden"
+    if not (gdir / "golden_gpu.pt").is_file():
+        pytest.skip("golden_gpu.pt not recorded yet")
+    fx = torch.load(gdir / "golden_gpu.pt")
+    p = torch.load(gdir / "golden_cpu.pt")["problem"]
+    c = {k: v.cuda() for k, v in p.items()}
+    for ef, (tI, tD) in fx["traverse"].items():
+        ours = _ours(c, ef, 32, packed=True)
+        same = sum(a == b for a, b in zip(topk_ids(*ours, 10), topk_ids(tI, tD, 10)))
+        assert same >= 0.95 * tI.size(0)       # 24 queries: at most one may differ
+    for (n_r, n_l), r in fx["routing"].items():
+        ev = p["full"][r["entry_nodes"]].contiguous()
+        router, dist = extension.routing_cuda(c["query"], r["route_vectors"].cuda(),
+                                              r["entry_nodes"].cuda(), ev.cuda())
+        assert torch.equal(router.cpu(), r["router"])
+        assert torch.allclose(dist.cpu(), r["distances"], rtol=1e-5, atol=0.0)
