@@ -156,6 +156,41 @@ int pa_stage_search_device(pa_stage *stage, const float *dev_query,
 int pa_stage_synchronize(pa_stage *stage);
 /* cudaStream_t of the stage's first stream (for event timing by the caller). */
 void *pa_stage_stream(pa_stage *stage);
+/* ---- search without any allocation -----------------------------------------
+ * No counterpart upstream (upstream allocates in every call: torch::zeros /
+ * torch::empty in routing_cuda.cu:96-98 and pipeline_cpu.cpp:78-96).  For callers
+ * that cannot allocate device memory at all: processes that gave the whole GPU to
+ * their own memory pool at start-up, and latency-critical threads that must not
+ * trigger the device-wide synchronisation cudaMalloc / cudaFree imply.
+ *
+ * Entry routing followed by traversal over the packed index, i.e. pa_route then
+ * pa_traverse_packed, with the intermediate entry tables kept in a static device
+ * array of PA_NOALLOC_SCRATCH_BYTES that every GPU loading the library holds
+ * until exit.  The caller passes inputs and outputs only: query [batch,
+ * d_principle] (already projected / reduced), outputs as pa_traverse_packed.
+ * route_vectors may be NULL (shared entry list, n_routers ignored).
+ *
+ * Limits: batch <= PA_NOALLOC_MAX_BATCH and n_leaves <= PA_NOALLOC_MAX_LEAVES,
+ * otherwise PA_ERR_ARG with a message naming the limit.  The call performs no
+ * cudaMalloc / cudaFree and calls no allocating library routine.  The first call
+ * on each device looks the array's address up (cudaGetSymbolAddress); make that
+ * first call before any stream capture.  All calls on a device share the one
+ * array, which keeps the previous call's contents (nothing in it needs to start
+ * at zero: the routing step overwrites every element the traversal reads);
+ * calls that overlap on the GPU -- different streams, or different host threads
+ * -- race on it, so serialise them. */
+#define PA_NOALLOC_MAX_BATCH 1024
+#define PA_NOALLOC_MAX_LEAVES 64
+#define PA_NOALLOC_SCRATCH_BYTES (PA_NOALLOC_MAX_BATCH * PA_NOALLOC_MAX_LEAVES * 12)
+int pa_search_reduced_noalloc(int64_t *output_I, float *output_D,
+                              const int32_t *packed_nbr, const int32_t *row_of,
+                              const float *storage, const float *query,
+                              const float *route_vectors, const int64_t *entry_nodes,
+                              const float *entry_vectors, int64_t batch,
+                              int64_t n_nodes, int64_t n_storage, int d_principle,
+                              int n_neighbors, int n_routers, int n_leaves,
+                              int ef_search, void *stream);
+
 /* Kernels launched by this library on behalf of the calling process. */
 int64_t pa_launch_count(void);
 

@@ -20,7 +20,7 @@ SYMBOLS = (
     "pa_version", "pa_last_error", "pa_heap_size_for", "pa_traverse_csr", "pa_pack_graph",
     "pa_traverse_packed", "pa_route", "pa_project", "pa_stage_create", "pa_stage_destroy",
     "pa_stage_search", "pa_stage_search_device", "pa_stage_synchronize", "pa_stage_stream",
-    "pa_launch_count",
+    "pa_launch_count", "pa_search_reduced_noalloc",
 )
 
 
@@ -67,6 +67,9 @@ def lib() -> ctypes.CDLL:
     L.pa_stage_stream.argtypes = [P]
     L.pa_stage_stream.restype = P
     L.pa_launch_count.restype = c_int64
+    L.pa_search_reduced_noalloc.argtypes = [P, P, P, P, P, P, P, P, P, c_int64, c_int64, c_int64,
+                                            c_int, c_int, c_int, c_int, c_int, P]
+    L.pa_search_reduced_noalloc.restype = c_int
     for name in ("pa_traverse_csr", "pa_pack_graph", "pa_traverse_packed", "pa_route",
                  "pa_project", "pa_stage_create", "pa_stage_search", "pa_stage_search_device",
                  "pa_stage_synchronize", "pa_heap_size_for"):

@@ -175,5 +175,42 @@ def project(query, VT, d_out: int | None = None):
     return out
 
 
+NOALLOC_MAX_BATCH = 1024
+NOALLOC_MAX_LEAVES = 64
+
+
+def search_reduced_noalloc(output_I, output_D, packed_nbr, row_of, storage, query,
+                           route_vectors, entry_nodes, entry_vectors, n_neighbors: int) -> None:
+    """Routing + traversal through ``pa_search_reduced_noalloc``: for callers that
+    must not allocate device memory (the GPU was handed to a private pool, or the
+    thread cannot afford the device-wide stall of an allocation).  This wrapper
+    creates no tensor either; everything, outputs included, comes from the
+    caller.  Limits: ``batch <= NOALLOC_MAX_BATCH``, ``n_leaves <=
+    NOALLOC_MAX_LEAVES``.  Calls on one device must not overlap."""
+    _check_cuda("packed_nbr", packed_nbr, 3, torch.int32)
+    _check_cuda("row_of", row_of, 1, torch.int32)
+    _check_cuda("storage", storage, 2, torch.float32)
+    _check_cuda("query", query, 2, torch.float32)
+    _check_cuda("output_I", output_I, 3, torch.int64)
+    _check_cuda("output_D", output_D, 3, torch.float32)
+    _check_cuda("entry_nodes", entry_nodes, 2 if route_vectors is not None else 1, torch.int64)
+    _check_cuda("entry_vectors", entry_vectors, 3 if route_vectors is not None else 2,
+                torch.float32)
+    if route_vectors is not None:
+        _check_cuda("route_vectors", route_vectors, 2, torch.float32)
+    batch, d = query.shape
+    _require(storage.size(1) == d, "storage.size(-1) == d_principle")
+    _require(output_I.shape == output_D.shape and output_I.size(0) == batch
+             and output_I.size(1) == BEAM_WIDTH, "output shape [batch, 4, ef]")
+    with torch.cuda.device(query.device):
+        _C.check(_C.lib().pa_search_reduced_noalloc(
+            output_I.data_ptr(), output_D.data_ptr(), packed_nbr.data_ptr(), row_of.data_ptr(),
+            storage.data_ptr(), query.data_ptr(),
+            0 if route_vectors is None else route_vectors.data_ptr(), entry_nodes.data_ptr(),
+            entry_vectors.data_ptr(), batch, row_of.size(0), storage.size(0), d, n_neighbors,
+            0 if route_vectors is None else route_vectors.size(0), entry_nodes.size(-1),
+            output_I.size(2), _stream(query.device)))
+
+
 def launch_count() -> int:
     return int(_C.lib().pa_launch_count())
