@@ -1,16 +1,34 @@
 // Multi-beam graph traversal in the reduced space -- the HBM-gather-bound hot
-// loop of the search stage.  One CTA of four warps per query, one warp per
-// beam, as in upstream extension/traverse_cuda.cu:45-246; the search semantics
-// (heap layouts, bloom hashing, dealing of candidates to beams, stop rules,
-// output order) are upstream's, executed in ONE fixed interleaving so that the
-// result is a deterministic function of the inputs:
-//   * the bloom filter is cleared, then seeded with the entries, then used;
-//   * in a round, beams test-and-set their neighbours in the order beam 0..3
-//     (a token passed over named barriers); a beam handles 32 neighbours at a
-//     time, running the four hash steps in lock step, and within a step lanes
-//     hitting the same bit are served in ascending lane order
-//     (__match_any_sync picks the first lane, the others see the bit as set);
-//   * each beam's heaps are touched by one lane only.
+// loop of the search stage.  One CTA of four warps per query.  The search
+// semantics (four beams, heap layouts, bloom hashing, dealing of candidates to
+// beams, stop rules, output order) are those of upstream
+// extension/traverse_cuda.cu:45-246, executed in ONE fixed interleaving so that
+// the result is a deterministic function of the inputs:
+//   * the bloom filter is cleared, then seeded with the admitted entries, then
+//     used;
+//   * in a round the neighbour slots are tested-and-set beam 0 -> 3, 32 slots
+//     at a time; a chunk of 32 runs the four hash steps in lock step and within
+//     a step lanes hitting the same bit are served in ascending lane order
+//     (__match_any_sync elects the first lane, the others see the bit as set);
+//   * each heap sees its operations in upstream's order.
+//
+// Work split inside the CTA (all four beams share every warp):
+//   warp 0  "open" warp: pops the four open heaps, fetches the four neighbour
+//           rows, runs the bloom filter and the compaction, and later applies
+//           heap_replace to the four open heaps;
+//   warp 1  "result" warp: applies heap_pushpop to the four result heaps and
+//           writes the output;
+//   all warps: 16 teams of 8 lanes evaluate the distances of a round.
+// A heap operation is executed by a group of 8 lanes, one lane per level of the
+// root-to-leaf path, the four beams side by side in one warp.  The path is not
+// found by walking keys in shared memory: each heap keeps, in registers, one bit
+// per internal node for "right child smaller" and (open heaps) one for "right
+// child larger"; following them is a few integer instructions, after which every
+// lane derives its own node of the path by a shift (1-based heap indices).  The
+// bits of the nodes whose children changed are refreshed with one redux per
+// word.  The element layout of the heaps is exactly upstream's after every
+// operation (heapq.cuh:13-87), which is what makes evictions -- and therefore
+// results -- identical.
 //
 // Two index layouts are served by the same kernel body:
 //   CsrLayout    -- upstream's tensors as they are (int64 indptr / indices /
@@ -21,11 +39,6 @@
 #include "pa_common.cuh"
 
 namespace pa {
-
-struct OpenVal {
-    int32_t node;  // global id, -1 = empty
-    int32_t row;   // storage row of `node` (packed layout), -1 = none
-};
 
 struct CsrLayout {
     static constexpr bool kPacked = false;
@@ -45,39 +58,195 @@ struct PackedLayout {
 };
 
 constexpr int kThreads = kBeams * 32;
+constexpr int kGroup = 8;  // lanes per heap operation
+constexpr unsigned kFull = 0xffffffffu;
 
-__device__ __forceinline__ void named_sync(int id, int n) {
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory");
-}
-__device__ __forceinline__ void named_arrive(int id, int n) {
-    asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(n) : "memory");
+template <int H> struct HeapShape {
+    static constexpr int kLog = (H == 32) ? 5 : (H == 64) ? 6 : (H == 128) ? 7 : 8;
+    // words covering the bits of nodes 1 .. H/2-1 (node H/2 has one child: bit 0)
+    static constexpr int kWords = H <= 64 ? 1 : H / 64;
+};
+
+// ---- comparison-bit words --------------------------------------------------
+// Bit n of a set belongs to heap node n (1-based); only nodes 1 .. H/2-1 (two
+// children) ever carry a set bit.  Nodes of levels 0-4 live in word 0, level 5
+// in word 1, level 6 in words 2 and 3.
+
+template <int I, int W>
+__device__ __forceinline__ uint32_t word_of(const uint32_t (&w)[W]) {
+    if constexpr (I < W) return w[I];
+    else return 0u;
 }
 
-// upstream traverse_cuda.cu:18-43: eight lanes, lane t owns floats
-// [32m + 4t, 32m + 4t + 4); acc += fma(dx,dx,dy*dy); acc += fma(dz,dz,dw*dw);
-// then the width-8 shuffle tree 4, 2, 1.  Result valid in the team's lane 0.
-__device__ __forceinline__ float team_distance(const float *__restrict__ row,
-                                               const float *__restrict__ q, int d, int t8,
-                                               bool pred) {
-    float acc = 0.0f;
-    if (pred) {
-        for (int off = 4 * t8; off < d; off += 32) {
-            float4 p = __ldg(reinterpret_cast<const float4 *>(row + off));
-            float4 c = *reinterpret_cast<const float4 *>(q + off);
-            float dx = __fsub_rn(c.x, p.x), dy = __fsub_rn(c.y, p.y);
-            float dz = __fsub_rn(c.z, p.z), dw = __fsub_rn(c.w, p.w);
-            acc = __fadd_rn(acc, __fmaf_rn(dx, dx, __fmul_rn(dy, dy)));
-            acc = __fadd_rn(acc, __fmaf_rn(dz, dz, __fmul_rn(dw, dw)));
-        }
+// bit of node n, n < 32 * W
+template <int W>
+__device__ __forceinline__ uint32_t bit_at(const uint32_t (&w)[W], unsigned n) {
+    uint32_t word = w[0];
+    if constexpr (W == 2) word = (n & 32u) ? w[1] : w[0];
+    if constexpr (W == 4) {
+        const uint32_t lo = (n & 32u) ? w[1] : w[0], hi = (n & 32u) ? w[3] : w[2];
+        word = (n & 64u) ? hi : lo;
     }
+    return (word >> (n & 31u)) & 1u;
+}
+
+// Leaf reached from the root by following the bits.
+template <int H, int W>
+__device__ __forceinline__ unsigned follow_bits(const uint32_t (&w)[W]) {
+    unsigned n = 1;
+#pragma unroll
+    for (int l = 0; l < HeapShape<H>::kLog - 1; ++l) {
+        uint32_t word;
+        if (l < 5) word = w[0];
+        else if (l == 5) word = word_of<1, W>(w);
+        else word = (n & 32u) ? word_of<3, W>(w) : word_of<2, W>(w);
+        n = 2u * n + ((word >> (n & 31u)) & 1u);
+    }
+    return n == H / 2 ? static_cast<unsigned>(H) : n;  // node H/2 has one child only
+}
+
+// XOR `mine` (a single bit, or 0) into the word that holds node n, combined
+// over the 8 lanes of a group.
+template <int W>
+__device__ __forceinline__ void flip_bits(uint32_t (&w)[W], unsigned gmask, uint32_t mine,
+                                          unsigned n) {
+    if constexpr (W == 1) {
+        w[0] ^= __reduce_or_sync(gmask, mine);
+    } else {
+#pragma unroll
+        for (int i = 0; i < W; ++i)
+            w[i] ^= __reduce_or_sync(gmask, (n >> 5) == static_cast<unsigned>(i) ? mine : 0u);
+    }
+}
+
+struct GroupCtx {
+    unsigned g;      // lane within the group = level handled
+    unsigned gmask;  // lanes of this group
+    unsigned gshift; // first lane of this group
+};
+
+// ---- heap operations, one group of 8 lanes per heap --------------------------
+// K / V: the heap's arrays in shared memory (0-based storage of 1-based nodes).
+// sb / lb: "right child smaller" / "right child larger" bits.
+
+// Puts (k, v) at the root and sinks it (upstream __heapify_up, heapq.cuh:13-29).
+// Used for heap_pushpop (after its root test) and heap_pop (k = +inf).
+// Returns the new root key (group-uniform; meaningful only for active groups).
+template <int H, int W, bool kHasLb, typename V>
+__device__ __forceinline__ float group_sink(float *K, V *Vv, uint32_t (&sb)[W], uint32_t (&lb)[W],
+                                            const GroupCtx &c, bool active, float k, V v) {
+    const unsigned leaf = follow_bits<H, W>(sb);
+    const unsigned L = 31u - __clz(leaf);
+    const unsigned t = c.g + 1u;  // this lane's level on the path
+    const bool on = active && t <= L;
+    const unsigned node = on ? (leaf >> (L - t)) : 2u;
+    const bool has_sib = node < static_cast<unsigned>(H);  // node H has no sibling
+    const bool sib_ok = on && has_sib;
+    const float a = on ? K[node - 1] : CUDART_INF_F;
+    const V av = Vv[node - 1];
+    const float sk = K[(has_sib ? (node ^ 1u) : node) - 1];
+    // children strictly smaller than the moving key move up one level
+    const unsigned cm = __ballot_sync(c.gmask, on && a < k) >> c.gshift;
+    const unsigned cnt = __ffs(~cm) - 1;  // number of leading levels that move
+    const float a_next = __shfl_down_sync(c.gmask, a, 1, kGroup);
+    const float a_first = __shfl_sync(c.gmask, a, 0, kGroup);
+    const bool moves = on && t <= cnt;
+    if (moves) { K[(node >> 1) - 1] = a; Vv[(node >> 1) - 1] = av; }
+    if (active && t == max(cnt, 1u)) {
+        // cnt == 0: the new element stays at the root (written by level-1 lane)
+        const unsigned at = cnt == 0 ? 1u : node;
+        K[at - 1] = k; Vv[at - 1] = v;
+    }
+    // refresh the bits of the parents of the moved nodes (path levels 0 .. cnt-1)
+    const float nk = (t == cnt) ? k : a_next;  // new key at this lane's node
+    const bool odd = node & 1u;
+    const float left = odd ? sk : nk, right = odd ? nk : sk;
+    const unsigned parent = node >> 1;
+    const bool upd = moves && sib_ok;
+    const uint32_t s_flip = (right < left) != (bit_at<W>(sb, parent) != 0);
+    flip_bits<W>(sb, c.gmask, (upd && s_flip) ? (1u << (parent & 31u)) : 0u, parent);
+    if constexpr (kHasLb) {
+        const uint32_t l_flip = (right > left) != (bit_at<W>(lb, parent) != 0);
+        flip_bits<W>(lb, c.gmask, (upd && l_flip) ? (1u << (parent & 31u)) : 0u, parent);
+    }
+    __syncwarp();
+    return cnt == 0 ? k : a_first;
+}
+
+// upstream heap_replace (heapq.cuh:47-77): walk to a leaf along the larger
+// child, give up if the new key is not smaller than that leaf, else overwrite it
+// and sift up while the parent is strictly larger.  group_replace_at is the
+// second half: `leaf` is the leaf the walk ends in and `accept` says whether
+// this group's key passed the test against it.
+template <int H, int W, typename V>
+__device__ __forceinline__ void group_replace_at(float *K, V *Vv, uint32_t (&sb)[W],
+                                                 uint32_t (&lb)[W], const GroupCtx &c,
+                                                 unsigned leaf, bool accept, float k, V v) {
+    const unsigned L = 31u - __clz(leaf);
+    const unsigned t = c.g;  // ancestors: levels 0 .. L-1
+    const bool on = accept && t < L;
+    const unsigned child = on ? (leaf >> (L - t - 1u)) : 2u;
+    const unsigned node = child >> 1;
+    const bool has_sib = child < static_cast<unsigned>(H);
+    const float b = K[node - 1];
+    const V bv = Vv[node - 1];
+    const float sk = K[(has_sib ? (child ^ 1u) : child) - 1];
+    // ancestors strictly larger than the new key move down one level
+    const unsigned cm = __ballot_sync(c.gmask, on && b > k) >> c.gshift;
+    const unsigned s = cm ? (__ffs(cm) - 1) : L;  // level where the new element lands
+    const bool moves = on && t >= s;
+    if (moves) { K[child - 1] = b; Vv[child - 1] = bv; }
+    if (accept && t == min(s, L - 1u)) {
+        // s == L: nothing moves, the new element replaces the leaf (level L-1 lane)
+        const unsigned at = s == L ? leaf : node;
+        K[at - 1] = k; Vv[at - 1] = v;
+    }
+    // parents whose path child changed: levels max(s-1, 0) .. L-1
+    const float nk = (t + 1u == s) ? k : b;  // new key of this lane's path child
+    const bool odd = child & 1u;
+    const float left = odd ? sk : nk, right = odd ? nk : sk;
+    const bool upd = on && t + 1u >= s && has_sib;
+    const bool s_flip = (right < left) != (bit_at<W>(sb, node) != 0);
+    const bool l_flip = (right > left) != (bit_at<W>(lb, node) != 0);
+    flip_bits<W>(sb, c.gmask, (upd && s_flip) ? (1u << (node & 31u)) : 0u, node);
+    flip_bits<W>(lb, c.gmask, (upd && l_flip) ? (1u << (node & 31u)) : 0u, node);
+    __syncwarp();
+}
+
+template <int H, int W, typename V>
+__device__ __forceinline__ void group_replace(float *K, V *Vv, uint32_t (&sb)[W],
+                                              uint32_t (&lb)[W], const GroupCtx &c, bool active,
+                                              float k, V v) {
+    const unsigned leaf = follow_bits<H, W>(lb);
+    const bool accept = active && k < K[leaf - 1];
+    if (!__any_sync(kFull, accept)) return;
+    group_replace_at<H, W>(K, Vv, sb, lb, c, leaf, accept, k, v);
+}
+
+// Next candidate of this group's beam, at or after position `s` of the beam's
+// list, whose distance is below `limit`; candidates are examined eight at a
+// time.  Returns the position (>= count if there is none).  Distances of
+// candidates that must not be inserted are stored as +inf.
+// ---- distance (upstream traverse_cuda.cu:18-43) -------------------------------
+// Eight lanes; lane t owns floats [32m + 4t, 32m + 4t + 4);
+// acc += fma(dx,dx,dy*dy); acc += fma(dz,dz,dw*dw); then the shuffle tree 4, 2, 1.
+__device__ __forceinline__ float stripe(float acc, float4 c, float4 p) {
+    const float dx = __fsub_rn(c.x, p.x), dy = __fsub_rn(c.y, p.y);
+    const float dz = __fsub_rn(c.z, p.z), dw = __fsub_rn(c.w, p.w);
+    acc = __fadd_rn(acc, __fmaf_rn(dx, dx, __fmul_rn(dy, dy)));
+    return __fadd_rn(acc, __fmaf_rn(dz, dz, __fmul_rn(dw, dw)));
+}
+
+__device__ __forceinline__ float team_reduce(float acc) {
 #pragma unroll
     for (int off = kTeam / 2; off > 0; off >>= 1)
-        acc = __fadd_rn(acc, __shfl_down_sync(0xffffffffu, acc, off, kTeam));
+        acc = __fadd_rn(acc, __shfl_down_sync(kFull, acc, off, kTeam));
     return acc;
 }
 
-// One chunk of 32 neighbours of one beam: test-and-set in the fixed order.
-// Returns true for lanes whose node was already present (or is invalid).
+// ---- bloom -----------------------------------------------------------------------
+// One chunk of 32 neighbours: test-and-set in the fixed order.  Returns true for
+// lanes whose node was already present (or is not a node).
 __device__ __forceinline__ bool bloom_visit(uint32_t *bloom, int32_t v, int lane) {
     const bool valid = v >= 0;
     uint32_t pos[kFnvSteps];
@@ -90,206 +259,378 @@ __device__ __forceinline__ bool bloom_visit(uint32_t *bloom, int32_t v, int lane
     bool found = true;
 #pragma unroll
     for (int s = 0; s < kFnvSteps; ++s) {
-        // invalid lanes get a key no valid lane can have
-        uint32_t key = valid ? pos[s] : (0x80000000u | lane);
-        uint32_t peers = __match_any_sync(0xffffffffu, key);
-        bool leader = (__ffs(peers) - 1) == lane;
+        // lanes without a node get a key no node can have
+        const uint32_t key = valid ? pos[s] : (0x80000000u | lane);
+        const uint32_t peers = __match_any_sync(kFull, key);
+        const bool leader = (__ffs(peers) - 1) == lane;
         if (valid && leader) {
-            uint32_t bit = 1u << (pos[s] & 31);
-            uint32_t old = atomicOr(&bloom[pos[s] >> 5], bit);
+            const uint32_t bit = 1u << (pos[s] & 31);
+            const uint32_t old = atomicOr(&bloom[pos[s] >> 5], bit);
             found = found && (old & bit);
         }
-        // non-leaders: a lower lane sets this very bit in this step -> seen as set
+        // others: a lower lane sets this very bit in this step -> seen as set
         __syncwarp();
     }
     return found || !valid;
 }
 
-template <int H, class Layout>
-__global__ void __launch_bounds__(kThreads)
+__device__ __forceinline__ void bloom_insert(uint32_t *bloom, int32_t v) {
+    uint32_t h = kFnvOffset;
+#pragma unroll
+    for (int s = 0; s < kFnvSteps; ++s) {
+        h = fnv1a_32(static_cast<uint32_t>(v), h);
+        const uint32_t p = h & (kBloomBits - 1);
+        atomicOr(&bloom[p >> 5], 1u << (p & 31));
+    }
+}
+
+__device__ __forceinline__ void pair_sync() {  // warps 0 and 1 only
+    asm volatile("bar.sync 1, 64;" ::: "memory");
+}
+
+// Candidates are dealt to the beams four at a time (candidate j -> beam
+// (j / 4) mod 4); beam 0 always holds the most.
+__device__ __forceinline__ int deal_steps(int n) { return 4 * (n >> 4) + min(4, n & 15); }
+__device__ __forceinline__ int deal_index(int s, int beam) {
+    return 16 * (s >> 2) + 4 * beam + (s & 3);
+}
+__device__ __forceinline__ int deal_count(int n, int beam) {
+    return 4 * (n >> 4) + min(4, max((n & 15) - 4 * beam, 0));
+}
+
+// Next candidate of this group's beam, at or after position `s` of the beam's
+// list, whose distance is below `limit`; the group examines eight candidates at
+// a time.  Returns the position (>= count if there is none).  Between two
+// accepted heap operations the acceptance limit of a heap does not change, so
+// skipping the candidates that fail it is exactly what running the operation on
+// each of them would do.
+__device__ __forceinline__ int next_below(const float *cand_d, const GroupCtx &c, int beam,
+                                          int s, int count, float limit) {
+    bool searching = s < count;
+    while (__any_sync(kFull, searching)) {
+        const int sc = s + static_cast<int>(c.g);
+        const float dist = (searching && sc < count) ? cand_d[deal_index(sc, beam)] : CUDART_INF_F;
+        const unsigned m = __ballot_sync(c.gmask, dist < limit) >> c.gshift;
+        if (searching) {
+            if (m) { s += __ffs(m) - 1; searching = false; }
+            else { s += kGroup; searching = s < count; }
+        }
+    }
+    return s;
+}
+
+template <int H, int CH, class Layout>
+__global__ void __launch_bounds__(kThreads, 8)
 traverse_kernel(Layout L, int64_t *__restrict__ out_I, float *__restrict__ out_D,
                 const float *__restrict__ query, const int64_t *__restrict__ init_I,
-                const float *__restrict__ init_D, int d, int64_t ldq, int n_nb, int n_init,
-                int ef, int32_t *__restrict__ stats) {
+                const float *__restrict__ init_D, int d, int64_t ldq, int n_init, int ef,
+                int32_t *__restrict__ stats) {
+    constexpr int W = HeapShape<H>::kWords;
+    constexpr int n_nb = 32 * CH;
     __shared__ uint32_t bloom[kBloomWords];
     __shared__ float open_key[kBeams][H];
-    __shared__ OpenVal open_val[kBeams][H];
+    __shared__ int2 open_val[kBeams][H];  // {global id, storage row}
     __shared__ float res_key[kBeams][H];
     __shared__ int32_t res_id[kBeams][H];
-    __shared__ int2 slots[kMaxSlots];
-    __shared__ int counts[kBeams];
+    __shared__ int2 slots[kBeams * n_nb];  // survivors {global id, storage row}
+    __shared__ float cand_d[kBeams * n_nb];
+    __shared__ int n_work_s;
     __shared__ int stat_s[4];
     extern __shared__ __align__(16) float q_s[];
 
     const int lane = threadIdx.x & 31;
     const int w = threadIdx.x >> 5;
     const int64_t b = blockIdx.x;
-    const int chunks = n_nb >> 5;  // 1 or 2
+    GroupCtx gc;
+    gc.g = lane & 7;
+    const int beam = lane >> 3;  // heap this lane's group works on
+    gc.gshift = beam * kGroup;
+    gc.gmask = 0xffu << gc.gshift;
 
     for (int i = threadIdx.x; i < kBloomWords; i += kThreads) bloom[i] = 0;
     for (int i = threadIdx.x; i < d; i += kThreads) q_s[i] = query[b * ldq + i];
-    for (int i = lane; i < H; i += 32) {
-        open_key[w][i] = CUDART_INF_F;
-        open_val[w][i] = OpenVal{-1, -1};
-        res_key[w][i] = -CUDART_INF_F;
-        res_id[w][i] = -1;
+    for (int i = threadIdx.x; i < kBeams * H; i += kThreads) {
+        (&open_key[0][0])[i] = CUDART_INF_F;
+        (&open_val[0][0])[i] = make_int2(-1, -1);
+        (&res_key[0][0])[i] = -CUDART_INF_F;
+        (&res_id[0][0])[i] = -1;
     }
     if (threadIdx.x < 4) stat_s[threadIdx.x] = 0;
     __syncthreads();
 
-    float *okey = open_key[w];
-    OpenVal *oval = open_val[w];
-    float *rkey = res_key[w];
-    int32_t *rid = res_id[w];
+    float *okey = open_key[beam];
+    int2 *oval = open_val[beam];
+    float *rkey = res_key[beam];
+    int32_t *rid = res_id[beam];
+    uint32_t o_sb[W], o_lb[W], r_sb[W];  // all keys equal at start: all bits 0
+#pragma unroll
+    for (int i = 0; i < W; ++i) o_sb[i] = o_lb[i] = r_sb[i] = 0;
+    float r_root = -CUDART_INF_F;  // warp 1: root key of the result heap
     int n_expand = 0, n_eval = 0, n_rounds = 0;
 
-    // ---- entries: entry i belongs to beam i mod 4 (traverse_cuda.cu:96-111).
-    // Loads are lane-parallel, the heap inserts run on lane 0 in entry order.
-    for (int base = 0; base * kBeams + w < n_init; base += 32) {
-        int i = (base + lane) * kBeams + w;
-        int64_t node = -1;
-        float dist = 0.0f;
-        int32_t row = -1;
-        if (i < n_init) {
-            node = init_I[b * n_init + i];
-            dist = init_D[b * n_init + i];
+    // ---- entries (traverse_cuda.cu:96-111): entry i belongs to beam i mod 4 ------
+    for (int base = 0; base < n_init; base += kThreads) {
+        const int n_here = min(kThreads, n_init - base);
+        if (threadIdx.x < n_here) {  // stage ids, rows, distances
+            const int i = threadIdx.x;
+            const int64_t node = init_I[b * n_init + base + i];
+            int32_t row = -1;
             if constexpr (Layout::kPacked) {
                 if (node >= 0 && node < L.n_nodes) row = __ldg(L.row_of + node);
             }
+            slots[i] = make_int2(node < 0 ? -1 : static_cast<int32_t>(node), row);
+            cand_d[i] = init_D[b * n_init + base + i];
         }
-        int todo = min(32, (n_init - w - base * kBeams + kBeams - 1) / kBeams);
-        for (int j = 0; j < todo; ++j) {
-            int64_t nj = __shfl_sync(0xffffffffu, node, j);
-            float dj = __shfl_sync(0xffffffffu, dist, j);
-            int32_t rj = __shfl_sync(0xffffffffu, row, j);
-            if (lane == 0 && nj >= 0 && !(dj >= -rkey[0])) {
-                heap_replace(okey, oval, H, dj, OpenVal{static_cast<int32_t>(nj), rj});
-                heap_pushpop(rkey, rid, H, -dj, static_cast<int32_t>(nj));
-                uint32_t h = kFnvOffset;
-#pragma unroll
-                for (int s = 0; s < kFnvSteps; ++s) {
-                    h = fnv1a_32(static_cast<uint32_t>(nj), h);
-                    uint32_t p = h & (kBloomBits - 1);
-                    atomicOr(&bloom[p >> 5], 1u << (p & 31));
+        __syncthreads();
+        const int steps = (n_here + kBeams - 1) / kBeams;
+        if (w == 1) {  // admission test (:99) + result heaps
+            for (int s = 0; s < steps; ++s) {
+                const int i = s * kBeams + beam;
+                const bool have = i < n_here;
+                const int2 e = have ? slots[i] : make_int2(-1, -1);
+                const float dist = have ? cand_d[i] : 0.0f;
+                const bool admit = have && e.x >= 0 && !(dist >= -r_root);
+                if (have && !admit && gc.g == 0) slots[i].x = -1;
+                const bool push = admit && (-dist > r_root);
+                if (__any_sync(kFull, push)) {
+                    const float root = group_sink<H, W, false>(rkey, rid, r_sb, r_sb, gc, push,
+                                                               -dist, e.x);
+                    if (push) r_root = root;
                 }
             }
+        }
+        __syncthreads();
+        if (w == 0) {  // open heaps
+            for (int s = 0; s < steps; ++s) {
+                const int i = s * kBeams + beam;
+                const bool have = i < n_here;
+                const int2 e = have ? slots[i] : make_int2(-1, -1);
+                const float dist = have ? cand_d[i] : 0.0f;
+                group_replace<H, W>(okey, oval, o_sb, o_lb, gc, have && e.x >= 0, dist, e);
+            }
+        } else if (w >= 2) {  // bloom: the union of the admitted entries' bits
+            for (int i = threadIdx.x - 64; i < n_here; i += kThreads - 64) {
+                const int32_t node = slots[i].x;
+                if (node >= 0) bloom_insert(bloom, node);
+            }
+        }
+        __syncthreads();
+    }
+
+    // ---- rounds (traverse_cuda.cu:179-226) -----------------------------------------
+    for (int step = 0; step < ef; ++step) {
+        ++n_rounds;
+        if (w == 0) {
+            // pop until every beam holds a node with an adjacency row, or gives up
+            // (:118-134)
+            int2 e[kBeams][CH];
+            int32_t u_node = -1, u_row = -1;
+            int64_t u_lo = 0;
+            int u_len = 0;
+            const float bound = -rkey[0];
+            bool pending = true;
+            bool fetch = false;  // this beam's row must be (re)loaded
+            // every pop removes one element, so H + 1 pops always settle a beam; the
+            // guards only bound the loops should that invariant ever be broken
+            for (int outer = 0; outer <= H + 1; ++outer) {
+                for (int guard = 0; guard <= H + 1 && __any_sync(kFull, pending); ++guard) {
+                    const float top_k = okey[0];
+                    const int2 top_v = oval[0];
+                    group_sink<H, W, true>(okey, oval, o_sb, o_lb, gc, pending, CUDART_INF_F,
+                                           make_int2(-1, -1));
+                    if (pending) {
+                        if (top_v.x < 0 || top_k >= bound) {
+                            pending = false; u_node = -1; u_row = -1; u_len = 0;
+                        } else if constexpr (Layout::kPacked) {
+                            if (top_v.y >= 0) { pending = false; u_node = top_v.x; u_row = top_v.y; }
+                        } else {
+                            const int64_t lo = __ldg(L.indptr + top_v.x);
+                            const int64_t hi = __ldg(L.indptr + top_v.x + 1);
+                            if (lo != hi) {
+                                pending = false; u_node = top_v.x; u_lo = lo;
+                                u_len = static_cast<int>(min(hi - lo, static_cast<int64_t>(n_nb)));
+                            }
+                        }
+                        if (!pending) fetch = true;
+                    }
+                }
+                // neighbour rows: lane i takes neighbour i (+32) of every beam
+                const unsigned fetch_any = __ballot_sync(kFull, fetch);
+#pragma unroll
+                for (int bb = 0; bb < kBeams; ++bb) {
+                    if (!((fetch_any >> (bb * kGroup)) & 1u)) continue;
+                    const int32_t node_b = __shfl_sync(kFull, u_node, bb * kGroup);
+                    if constexpr (Layout::kPacked) {
+                        const int32_t row_b = __shfl_sync(kFull, u_row, bb * kGroup);
+#pragma unroll
+                        for (int c = 0; c < CH; ++c)
+                            e[bb][c] = node_b >= 0
+                                ? __ldg(L.nbr + static_cast<int64_t>(row_b) * n_nb + 32 * c + lane)
+                                : make_int2(-1, -1);
+                    } else {
+                        const int64_t lo_b = __shfl_sync(kFull, u_lo, bb * kGroup);
+                        const int len_b = __shfl_sync(kFull, u_len, bb * kGroup);
+#pragma unroll
+                        for (int c = 0; c < CH; ++c) {
+                            const int i = 32 * c + lane;
+                            e[bb][c] = (node_b >= 0 && i < len_b)
+                                ? make_int2(static_cast<int32_t>(__ldg(L.indices + lo_b + i)), -1)
+                                : make_int2(-1, -1);
+                        }
+                    }
+                }
+                fetch = false;
+                if constexpr (Layout::kPacked) {
+                    // a sampled node whose adjacency row is empty: pop again
+#pragma unroll
+                    for (int bb = 0; bb < kBeams; ++bb) {
+                        const int tag = __shfl_sync(kFull, e[bb][0].x, 0);
+                        if (bb == beam && u_node >= 0 && tag == kEmptyRowTag) {
+                            pending = true; u_node = -1;
+                        }
+                    }
+                    if (!__any_sync(kFull, pending)) break;
+                } else {
+                    break;
+                }
+            }
+            n_expand += __popc(__ballot_sync(kFull, gc.g == 0 && u_node >= 0));
+
+            // bloom test-and-set in slot order, then compaction (:137-171)
+            int off = 0;
+#pragma unroll
+            for (int bb = 0; bb < kBeams; ++bb) {
+#pragma unroll
+                for (int c = 0; c < CH; ++c) {
+                    const bool seen = bloom_visit(bloom, e[bb][c].x, lane);
+                    const unsigned m = __ballot_sync(kFull, !seen);
+                    if (!seen) slots[off + __popc(m & ((1u << lane) - 1u))] = e[bb][c];
+                    off += __popc(m);
+                }
+            }
+            if (lane == 0) n_work_s = off;
+        }
+        __syncthreads();
+        const int n_work = n_work_s;
+        if (n_work < kTeamsPerWarp) break;  // :182-184, uniform over the CTA
+
+        // distances (:187-204): 16 teams of 8 lanes, two candidates in flight each.
+        // The loop bound is the same for every lane of a warp (the team shuffles
+        // below name the whole warp); lanes past the end carry a false predicate.
+        {
+            const int t8 = lane & 7;
+            for (int jb = w * kTeamsPerWarp; jb < n_work; jb += 2 * kBeams * kTeamsPerWarp) {
+                const int j0 = jb + (lane >> 3);
+                const int j1 = j0 + kBeams * kTeamsPerWarp;
+                const bool p0_in = j0 < n_work, p1_in = j1 < n_work;
+                int2 s0 = p0_in ? slots[j0] : make_int2(-1, -1);
+                int2 s1 = p1_in ? slots[j1] : make_int2(-1, -1);
+                if constexpr (!Layout::kPacked) {
+                    if (p0_in) s0.y = static_cast<int32_t>(__ldg(L.mapping + s0.x));
+                    if (p1_in) s1.y = static_cast<int32_t>(__ldg(L.mapping + s1.x));
+                    if (t8 == 0) {
+                        if (p0_in) slots[j0].y = s0.y;
+                        if (p1_in) slots[j1].y = s1.y;
+                    }
+                }
+                const bool p0 = p0_in && s0.y >= 0, p1 = p1_in && s1.y >= 0;
+                const float *r0 = L.storage + static_cast<int64_t>(p0 ? s0.y : 0) * d;
+                const float *r1 = L.storage + static_cast<int64_t>(p1 ? s1.y : 0) * d;
+                float a0 = 0.0f, a1 = 0.0f;
+                for (int o = 4 * t8; o < d; o += 64) {
+                    // two stripes of each row in flight before any arithmetic
+                    const bool second = o + 32 < d;
+                    float4 x0 = make_float4(0, 0, 0, 0), x1 = x0, y0 = x0, y1 = x0;
+                    if (p0) {
+                        x0 = __ldg(reinterpret_cast<const float4 *>(r0 + o));
+                        if (second) y0 = __ldg(reinterpret_cast<const float4 *>(r0 + o + 32));
+                    }
+                    if (p1) {
+                        x1 = __ldg(reinterpret_cast<const float4 *>(r1 + o));
+                        if (second) y1 = __ldg(reinterpret_cast<const float4 *>(r1 + o + 32));
+                    }
+                    const float4 qa = *reinterpret_cast<const float4 *>(q_s + o);
+                    if (p0) a0 = stripe(a0, qa, x0);
+                    if (p1) a1 = stripe(a1, qa, x1);
+                    if (second) {
+                        const float4 qb = *reinterpret_cast<const float4 *>(q_s + o + 32);
+                        if (p0) a0 = stripe(a0, qb, y0);
+                        if (p1) a1 = stripe(a1, qb, y1);
+                    }
+                }
+                a0 = team_reduce(a0);
+                a1 = team_reduce(a1);
+                // +inf marks a candidate without a vector: it is never inserted
+                if (t8 == 0) {
+                    if (p0_in) cand_d[j0] = p0 ? a0 : CUDART_INF_F;
+                    if (p1_in) cand_d[j1] = p1 ? a1 : CUDART_INF_F;
+                }
+            }
+        }
+        __syncthreads();
+
+        // heap inserts (:206-220): candidate j -> beam (j / 4) mod 4, ascending j.
+        // Each group walks its beam's list, skipping the candidates its heap would
+        // turn down, so that a step of the warp is an operation that changes a heap.
+        if (w < 2) {
+            const int count = deal_count(n_work, beam);
+            int s = 0;
+            if (w == 0) {
+                int valid = 0;
+                for (int j = lane; j < n_work; j += 32) valid += slots[j].y >= 0;
+                n_eval += __reduce_add_sync(kFull, valid);
+                unsigned leaf = follow_bits<H, W>(o_lb);
+                float limit = okey[leaf - 1];
+                for (;;) {
+                    s = next_below(cand_d, gc, beam, s, count, limit);
+                    const bool found = s < count;
+                    if (!__any_sync(kFull, found)) break;
+                    const int j = found ? deal_index(s, beam) : 0;
+                    group_replace_at<H, W>(okey, oval, o_sb, o_lb, gc, leaf, found, cand_d[j],
+                                           slots[j]);
+                    s += found;
+                    leaf = follow_bits<H, W>(o_lb);
+                    limit = okey[leaf - 1];
+                }
+            } else {
+                for (;;) {
+                    s = next_below(cand_d, gc, beam, s, count, -r_root);
+                    const bool found = s < count;
+                    if (!__any_sync(kFull, found)) break;
+                    const int j = found ? deal_index(s, beam) : 0;
+                    const float root = group_sink<H, W, false>(rkey, rid, r_sb, r_sb, gc, found,
+                                                               -cand_d[j], slots[j].x);
+                    if (found) { r_root = root; ++s; }
+                }
+            }
+            pair_sync();  // result roots visible to the open warp before it pops
         }
     }
     __syncthreads();
 
-    // ---- rounds (traverse_cuda.cu:179-226) ----------------------------------
-    for (int step = 0; step < ef; ++step) {
-        ++n_rounds;
-        // pop until a node with an adjacency row turns up (:118-134)
-        int32_t v0 = -1, v1 = -1, r0 = -1, r1 = -1;  // this lane's neighbours
-        bool expanding = false;
-        for (;;) {
-            float key = 0.0f;
-            OpenVal val{-1, -1};
-            if (lane == 0) {
-                heap_pop(okey, oval, H, OpenVal{-1, -1}, key, val);
-                if (val.node >= 0 && key >= -rkey[0]) val.node = -1;
-            }
-            int32_t node = __shfl_sync(0xffffffffu, val.node, 0);
-            if (node < 0) break;
-            if constexpr (Layout::kPacked) {
-                int32_t row = __shfl_sync(0xffffffffu, val.row, 0);
-                if (row < 0) continue;  // outside the sample: no adjacency
-                const int2 *src = L.nbr + static_cast<int64_t>(row) * n_nb;
-                int2 e0 = __ldg(src + lane);
-                if (__shfl_sync(0xffffffffu, e0.x, 0) == kEmptyRowTag) continue;
-                v0 = e0.x; r0 = e0.y;
-                if (chunks > 1) { int2 e1 = __ldg(src + 32 + lane); v1 = e1.x; r1 = e1.y; }
-            } else {
-                int64_t lo = 0, hi = 0;
-                if (lane == 0) { lo = __ldg(L.indptr + node); hi = __ldg(L.indptr + node + 1); }
-                lo = __shfl_sync(0xffffffffu, lo, 0);
-                hi = __shfl_sync(0xffffffffu, hi, 0);
-                if (lo == hi) continue;
-                if (lo + lane < hi) v0 = static_cast<int32_t>(__ldg(L.indices + lo + lane));
-                if (chunks > 1 && lo + 32 + lane < hi)
-                    v1 = static_cast<int32_t>(__ldg(L.indices + lo + 32 + lane));
-            }
-            expanding = true;
-            break;
+    // ---- store (:230-245): per beam worst -> best ----------------------------------
+    if (w == 1) {
+        int64_t *oI = out_I + (b * kBeams + beam) * ef;
+        float *oD = out_D + (b * kBeams + beam) * ef;
+        const int n_discard = max(H - ef, 0), n_real = min(ef, H);
+        for (int p = 0; p < n_discard + n_real; ++p) {
+            const float key = rkey[0];
+            const int32_t id = rid[0];
+            group_sink<H, W, false>(rkey, rid, r_sb, r_sb, gc, true, CUDART_INF_F, int32_t(-1));
+            const int i = p - n_discard;
+            if (i >= 0 && gc.g == 0) { oI[i] = id; oD[i] = -key; }
         }
-        if (expanding) ++n_expand;
-
-        // bloom test-and-set, beams in order (token over named barriers 1..3)
-        if (w > 0) named_sync(w, 64);
-        bool seen0 = bloom_visit(bloom, v0, lane);
-        bool seen1 = true;
-        if (chunks > 1) seen1 = bloom_visit(bloom, v1, lane);
-        if (w < kBeams - 1) named_arrive(w + 1, 64);
-
-        // compaction in slot order (:151-171)
-        uint32_t m0 = __ballot_sync(0xffffffffu, !seen0);
-        uint32_t m1 = __ballot_sync(0xffffffffu, !seen1);
-        if (lane == 0) counts[w] = __popc(m0) + __popc(m1);
-        __syncthreads();
-        int before = 0, n_work = 0;
-#pragma unroll
-        for (int i = 0; i < kBeams; ++i) {
-            int c = counts[i];
-            if (i < w) before += c;
-            n_work += c;
-        }
-        const uint32_t lt = (1u << lane) - 1u;
-        if (!seen0) slots[before + __popc(m0 & lt)] = make_int2(v0, r0);
-        if (!seen1) slots[before + __popc(m0) + __popc(m1 & lt)] = make_int2(v1, r1);
-        __syncthreads();
-        if (n_work < kTeamsPerWarp) break;  // :182-184, uniform over the CTA
-
-        // distances and heap inserts (:187-224): survivor j -> beam (j/4) mod 4,
-        // team j mod 4; a beam inserts its survivors in ascending j
-        const int team = lane >> 3, t8 = lane & 7;
-        for (int j0 = w * kTeamsPerWarp; j0 < n_work; j0 += kBeams * kTeamsPerWarp) {
-            int j = j0 + team;
-            bool pred = j < n_work;
-            int2 s = pred ? slots[j] : make_int2(-1, -1);
-            int64_t row;
-            if constexpr (Layout::kPacked) row = s.y;
-            else row = pred ? __ldg(L.mapping + s.x) : -1;
-            pred = pred && row >= 0;
-            float dist = team_distance(L.storage + row * d, q_s, d, t8, pred);
-#pragma unroll
-            for (int i = 0; i < kTeamsPerWarp; ++i) {
-                float di = __shfl_sync(0xffffffffu, dist, i * kTeam);
-                int32_t ni = __shfl_sync(0xffffffffu, s.x, i * kTeam);
-                int32_t ri = __shfl_sync(0xffffffffu, static_cast<int32_t>(row), i * kTeam);
-                int pi = __shfl_sync(0xffffffffu, static_cast<int>(pred), i * kTeam);
-                if (lane == 0 && pi) {
-                    heap_replace(okey, oval, H, di, OpenVal{ni, ri});
-                    heap_pushpop(rkey, rid, H, -di, ni);
-                    ++n_eval;
-                }
-            }
-        }
-    }
-
-    // ---- store (:230-245): per beam worst -> best ----------------------------
-    if (lane == 0) {
-        float key;
-        int32_t id;
-        for (int i = ef; i < H; ++i) heap_pop(rkey, rid, H, -1, key, id);
-        int64_t *oI = out_I + (b * kBeams + w) * ef;
-        float *oD = out_D + (b * kBeams + w) * ef;
-        for (int i = 0; i < ef; ++i) {
-            heap_pop(rkey, rid, H, -1, key, id);
-            oI[i] = id;
-            oD[i] = -key;
-        }
+        // ef > H: the heap is exhausted, upstream keeps popping (-1, key +inf)
+        for (int i = H + gc.g; i < ef; i += kGroup) { oI[i] = -1; oD[i] = -CUDART_INF_F; }
     }
     if (stats != nullptr) {
         __syncthreads();
         int bits = 0;
         for (int i = threadIdx.x; i < kBloomWords; i += kThreads) bits += __popc(bloom[i]);
-        for (int off = 16; off > 0; off >>= 1) bits += __shfl_down_sync(0xffffffffu, bits, off);
+        for (int o = 16; o > 0; o >>= 1) bits += __shfl_down_sync(kFull, bits, o);
         if (lane == 0) {
-            atomicAdd(&stat_s[1], n_expand);
-            atomicAdd(&stat_s[2], n_eval);
             atomicAdd(&stat_s[3], bits);
-            if (w == 0) stat_s[0] = n_rounds;
+            if (w == 0) { stat_s[0] = n_rounds; stat_s[1] = n_expand; stat_s[2] = n_eval; }
         }
         __syncthreads();
         if (threadIdx.x < 4) stats[b * 4 + threadIdx.x] = stat_s[threadIdx.x];
@@ -303,16 +644,21 @@ static int launch(Layout L, int64_t *out_I, float *out_D, const float *query, in
     if (batch == 0) return PA_OK;
     dim3 grid(static_cast<unsigned>(batch)), block(kThreads);
     size_t dyn = sizeof(float) * d;
-#define PA_LAUNCH(HS)                                                                    \
-    traverse_kernel<HS, Layout><<<grid, block, dyn, stream>>>(L, out_I, out_D, query,   \
-                                                              init_I, init_D, d, ldq,   \
-                                                              n_nb, n_init, ef, stats)
+#define PA_LAUNCH(HS, CHS)                                                  \
+    traverse_kernel<HS, CHS, Layout><<<grid, block, dyn, stream>>>(         \
+        L, out_I, out_D, query, init_I, init_D, d, ldq, n_init, ef, stats)
+#define PA_LAUNCH_H(HS)                                                     \
+    do {                                                                    \
+        if (n_nb == 32) PA_LAUNCH(HS, 1);                                   \
+        else PA_LAUNCH(HS, 2);                                              \
+    } while (0)
     switch (pa_heap_size_for(ef)) {
-        case 32: PA_LAUNCH(32); break;
-        case 64: PA_LAUNCH(64); break;
-        case 128: PA_LAUNCH(128); break;
-        default: PA_LAUNCH(256); break;
+        case 32: PA_LAUNCH_H(32); break;
+        case 64: PA_LAUNCH_H(64); break;
+        case 128: PA_LAUNCH_H(128); break;
+        default: PA_LAUNCH_H(256); break;
     }
+#undef PA_LAUNCH_H
 #undef PA_LAUNCH
     count_launch();
     PA_CUDA_TRY(cudaGetLastError());
@@ -327,7 +673,7 @@ static int check_common(const void *out_I, const void *out_D, const float *stora
     PA_REQUIRE(n_nb > 0 && n_nb % 32 == 0, "n_neighbors must be a multiple of 32");
     PA_REQUIRE(kBeams * n_nb <= kMaxSlots, "4 * n_neighbors must not exceed 256");
     PA_REQUIRE(d > 0 && d % 4 == 0, "d_model must be a positive multiple of 4");
-    PA_REQUIRE(d <= 8192, "d_model too large for the shared-memory query");
+    PA_REQUIRE(d <= 4096, "d_model too large for the shared-memory query");
     PA_REQUIRE(n_init >= 0, "n_initials must not be negative");
     PA_REQUIRE(n_nodes >= 0 && n_nodes < 0x7fffffff, "node ids must fit int32");
     if (batch == 0) return PA_OK;

@@ -8,7 +8,9 @@ padding at the tail of each row (``graphs.py:59-76``) -- and a graph of the same
 family: nodes are inserted in batches, every new node takes its candidates from
 an exact nearest-neighbour scan of the nodes inserted so far, selects up to
 ``n_neighbors`` of them with the HNSW diversity heuristic, and is linked back
-from each selected neighbour (re-pruning lists that overflow).  Early nodes keep
+from each selected neighbour (re-pruning lists that overflow); slots the
+heuristic leaves free are filled with the nearest pruned candidates (the
+"keep pruned connections" option of HNSW implementations).  Early nodes keep
 the long-range links they acquired while the graph was small, which is what
 makes the result navigable.  Everything is expressed in torch tensor ops and
 runs on whichever device ``x`` lives on (a GPU for million-scale inputs).
@@ -34,7 +36,7 @@ def _pairwise_sq(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
 
 
 def _select_diverse(cand: torch.Tensor, cand_d: torch.Tensor, x: torch.Tensor,
-                    max_keep: int) -> tuple[torch.Tensor, torch.Tensor]:
+                    max_keep: int, keep_pruned: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
     """HNSW neighbour-selection heuristic, batched.
 
     cand [b, C] candidate ids sorted by ascending distance to the owner (``-1``
@@ -53,6 +55,17 @@ def _select_diverse(cand: torch.Tensor, cand_d: torch.Tensor, x: torch.Tensor,
         take = valid[:, i] & ~blocked & (count < max_keep)
         kept[:, i] = take
         count += take.long()
+    if keep_pruned:
+        # fill the free slots with the nearest pruned candidates (kept ones first)
+        rank = torch.where(kept, 0, torch.where(valid, 1, 2)).to(torch.int8)
+        order = torch.argsort(rank, dim=1, stable=True)[:, :max_keep]
+        out_i = torch.gather(cand, 1, order)
+        out_d = torch.gather(cand_d, 1, order)
+        ok = torch.gather(valid, 1, order)
+        out_i = torch.where(ok, out_i, torch.full_like(out_i, -1))
+        out_d = torch.where(ok, out_d, torch.full_like(out_d, float("inf")))
+        resort = torch.argsort(out_d, dim=1, stable=True)
+        return torch.gather(out_i, 1, resort), torch.gather(out_d, 1, resort)
     # stable left-compaction of the kept candidates
     order = torch.argsort((~kept).to(torch.int8), dim=1, stable=True)[:, :max_keep]
     out_i = torch.gather(cand, 1, order)
@@ -84,7 +97,7 @@ def _topk_candidates(x: torch.Tensor, lo: int, hi: int, n_cand: int,
 @torch.no_grad()
 def build_graph(x: torch.Tensor, n_neighbors: int, ef_construct: int = 80,
                 first_batch: int = 1024, growth: float = 1.5,
-                chunk_bytes: int = 1 << 30) -> torch.Tensor:
+                chunk_bytes: int = 1 << 30, keep_pruned: bool = False) -> torch.Tensor:
     """Returns the adjacency as an int64 tensor [N, n_neighbors], ``-1`` padded."""
     assert x.dim() == 2
     N, d = x.shape
@@ -105,20 +118,21 @@ def build_graph(x: torch.Tensor, n_neighbors: int, ef_construct: int = 80,
         rev_src, rev_dst, rev_d = [], [], []
         for s in range(0, hi - lo, prune_rows):
             e = min(hi - lo, s + prune_rows)
-            sel_i, sel_d = _select_diverse(cand[s:e], cand_d[s:e], x, M)
+            sel_i, sel_d = _select_diverse(cand[s:e], cand_d[s:e], x, M, keep_pruned)
             adj[lo + s:lo + e] = sel_i
             adj_d[lo + s:lo + e] = sel_d
             owner = torch.arange(lo + s, lo + e, device=dev).unsqueeze(1).expand_as(sel_i)
             m = sel_i >= 0
             rev_src.append(owner[m]); rev_dst.append(sel_i[m]); rev_d.append(sel_d[m])
         _add_reverse_links(adj, adj_d, x, torch.cat(rev_dst), torch.cat(rev_src),
-                           torch.cat(rev_d), prune_rows)
+                           torch.cat(rev_d), prune_rows, keep_pruned)
         lo = hi
         hi = min(N, max(hi + first_batch, int(hi * growth)))
     return adj
 
 
-def _add_reverse_links(adj, adj_d, x, dst, src, dist, prune_rows: int) -> None:
+def _add_reverse_links(adj, adj_d, x, dst, src, dist, prune_rows: int,
+                       keep_pruned: bool = False) -> None:
     """Give every ``dst`` node a link to ``src`` (distance ``dist``); lists that
     overflow are re-selected with the diversity heuristic over old + new."""
     M = adj.size(1)
@@ -157,7 +171,7 @@ def _add_reverse_links(adj, adj_d, x, dst, src, dist, prune_rows: int) -> None:
         new_i = all_i[:, :M].clone()
         new_d = all_d[:, :M].clone()
         if (~fits).any():
-            sel_i, sel_d = _select_diverse(all_i[~fits], all_d[~fits], x, M)
+            sel_i, sel_d = _select_diverse(all_i[~fits], all_d[~fits], x, M, keep_pruned)
             new_i[~fits] = sel_i
             new_d[~fits] = sel_d
         adj[nodes] = new_i
@@ -173,7 +187,8 @@ def graph_init(x: torch.Tensor, graph_type: str, n_neighbors: int,
     if graph_type not in ("nsw", "nsg"):
         raise RuntimeError(graph_type)
     n_cand = ef_construct if graph_type == "nsw" else max(ef_construct, 3 * n_neighbors)
-    adj = build_graph(x, n_neighbors, ef_construct=n_cand)
+    chunk = (8 << 30) if x.is_cuda else (1 << 30)
+    adj = build_graph(x, n_neighbors, ef_construct=n_cand, chunk_bytes=chunk, keep_pruned=True)
     N = x.size(0)
     indptr = torch.arange(N + 1, dtype=torch.long) * n_neighbors
     return indptr, adj.reshape(-1).cpu()
