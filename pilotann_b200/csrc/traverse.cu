@@ -245,33 +245,48 @@ __device__ __forceinline__ float team_reduce(float acc) {
 }
 
 // ---- bloom -----------------------------------------------------------------------
-// One chunk of 32 neighbours: test-and-set in the fixed order.  Returns true for
-// lanes whose node was already present (or is not a node).
-__device__ __forceinline__ bool bloom_visit(uint32_t *bloom, int32_t v, int lane) {
-    const bool valid = v >= 0;
+// One chunk of 32 neighbours, test-and-set in the fixed order, in two parts.
+// bloom_prepare: the four bit positions of this lane's node and, per hash step,
+// whether this lane is the first (lowest) lane of the chunk that touches its bit
+// in that step.  bloom_commit: the serial part -- per step the elected lanes
+// atomically set their bit and learn whether it was set before; a lane that was
+// not elected has a lower lane setting the very same bit in the same step, so it
+// sees the bit as set.  Returns true for lanes whose node was already present
+// (or is not a node).
+struct BloomProbe {
     uint32_t pos[kFnvSteps];
+    uint32_t elected;  // bit s: this lane performs the atomic of step s
+};
+
+__device__ __forceinline__ BloomProbe bloom_prepare(int32_t v, int lane) {
+    BloomProbe p;
+    const bool valid = v >= 0;
     uint32_t h = kFnvOffset;
+    p.elected = 0;
 #pragma unroll
     for (int s = 0; s < kFnvSteps; ++s) {
         h = fnv1a_32(static_cast<uint32_t>(v), h);
-        pos[s] = h & (kBloomBits - 1);
+        p.pos[s] = h & (kBloomBits - 1);
+        // lanes without a node get a key no node can have
+        const uint32_t key = valid ? p.pos[s] : (0x80000000u | lane);
+        const uint32_t peers = __match_any_sync(kFull, key);
+        if (valid && (peers & ((1u << lane) - 1u)) == 0) p.elected |= 1u << s;
     }
+    return p;
+}
+
+__device__ __forceinline__ bool bloom_commit(uint32_t *bloom, const BloomProbe &p) {
     bool found = true;
 #pragma unroll
     for (int s = 0; s < kFnvSteps; ++s) {
-        // lanes without a node get a key no node can have
-        const uint32_t key = valid ? pos[s] : (0x80000000u | lane);
-        const uint32_t peers = __match_any_sync(kFull, key);
-        const bool leader = (__ffs(peers) - 1) == lane;
-        if (valid && leader) {
-            const uint32_t bit = 1u << (pos[s] & 31);
-            const uint32_t old = atomicOr(&bloom[pos[s] >> 5], bit);
+        if ((p.elected >> s) & 1u) {
+            const uint32_t bit = 1u << (p.pos[s] & 31);
+            const uint32_t old = atomicOr(&bloom[p.pos[s] >> 5], bit);
             found = found && (old & bit);
         }
-        // others: a lower lane sets this very bit in this step -> seen as set
         __syncwarp();
     }
-    return found || !valid;
+    return found;
 }
 
 __device__ __forceinline__ void bloom_insert(uint32_t *bloom, int32_t v) {
@@ -320,7 +335,7 @@ __device__ __forceinline__ int next_below(const float *cand_d, const GroupCtx &c
 }
 
 template <int H, int CH, class Layout>
-__global__ void __launch_bounds__(kThreads, 8)
+__global__ void __launch_bounds__(kThreads, 7)
 traverse_kernel(Layout L, int64_t *__restrict__ out_I, float *__restrict__ out_D,
                 const float *__restrict__ query, const int64_t *__restrict__ init_I,
                 const float *__restrict__ init_D, int d, int64_t ldq, int n_init, int ef,
@@ -496,13 +511,20 @@ traverse_kernel(Layout L, int64_t *__restrict__ out_I, float *__restrict__ out_D
             }
             n_expand += __popc(__ballot_sync(kFull, gc.g == 0 && u_node >= 0));
 
-            // bloom test-and-set in slot order, then compaction (:137-171)
+            // bloom test-and-set in slot order, then compaction (:137-171).  Hashes and
+            // the same-bit elections of a chunk do not depend on the filter's state, so
+            // they are computed before the serial chain of atomics.
             int off = 0;
+            BloomProbe probe[kBeams][CH];
+#pragma unroll
+            for (int bb = 0; bb < kBeams; ++bb)
+#pragma unroll
+                for (int c = 0; c < CH; ++c) probe[bb][c] = bloom_prepare(e[bb][c].x, lane);
 #pragma unroll
             for (int bb = 0; bb < kBeams; ++bb) {
 #pragma unroll
                 for (int c = 0; c < CH; ++c) {
-                    const bool seen = bloom_visit(bloom, e[bb][c].x, lane);
+                    const bool seen = bloom_commit(bloom, probe[bb][c]);
                     const unsigned m = __ballot_sync(kFull, !seen);
                     if (!seen) slots[off + __popc(m & ((1u << lane) - 1u))] = e[bb][c];
                     off += __popc(m);
@@ -537,25 +559,24 @@ traverse_kernel(Layout L, int64_t *__restrict__ out_I, float *__restrict__ out_D
                 const float *r0 = L.storage + static_cast<int64_t>(p0 ? s0.y : 0) * d;
                 const float *r1 = L.storage + static_cast<int64_t>(p1 ? s1.y : 0) * d;
                 float a0 = 0.0f, a1 = 0.0f;
-                for (int o = 4 * t8; o < d; o += 64) {
-                    // two stripes of each row in flight before any arithmetic
-                    const bool second = o + 32 < d;
-                    float4 x0 = make_float4(0, 0, 0, 0), x1 = x0, y0 = x0, y1 = x0;
-                    if (p0) {
-                        x0 = __ldg(reinterpret_cast<const float4 *>(r0 + o));
-                        if (second) y0 = __ldg(reinterpret_cast<const float4 *>(r0 + o + 32));
+                for (int o = 4 * t8; o < d; o += 128) {
+                    // up to four stripes of each row in flight before any arithmetic
+                    float4 x0[4], x1[4];
+#pragma unroll
+                    for (int m = 0; m < 4; ++m) {
+                        const bool in = o + 32 * m < d;
+                        x0[m] = (p0 && in) ? __ldg(reinterpret_cast<const float4 *>(r0 + o + 32 * m))
+                                           : make_float4(0, 0, 0, 0);
+                        x1[m] = (p1 && in) ? __ldg(reinterpret_cast<const float4 *>(r1 + o + 32 * m))
+                                           : make_float4(0, 0, 0, 0);
                     }
-                    if (p1) {
-                        x1 = __ldg(reinterpret_cast<const float4 *>(r1 + o));
-                        if (second) y1 = __ldg(reinterpret_cast<const float4 *>(r1 + o + 32));
-                    }
-                    const float4 qa = *reinterpret_cast<const float4 *>(q_s + o);
-                    if (p0) a0 = stripe(a0, qa, x0);
-                    if (p1) a1 = stripe(a1, qa, x1);
-                    if (second) {
-                        const float4 qb = *reinterpret_cast<const float4 *>(q_s + o + 32);
-                        if (p0) a0 = stripe(a0, qb, y0);
-                        if (p1) a1 = stripe(a1, qb, y1);
+#pragma unroll
+                    for (int m = 0; m < 4; ++m) {
+                        if (o + 32 * m < d) {
+                            const float4 qa = *reinterpret_cast<const float4 *>(q_s + o + 32 * m);
+                            a0 = stripe(a0, qa, x0[m]);
+                            a1 = stripe(a1, qa, x1[m]);
+                        }
                     }
                 }
                 a0 = team_reduce(a0);
