@@ -105,23 +105,33 @@ __device__ __forceinline__ unsigned follow_bits(const uint32_t (&w)[W]) {
     return n == H / 2 ? static_cast<unsigned>(H) : n;  // node H/2 has one child only
 }
 
+// OR over the 8 lanes of a group.  Warp collectives are always issued with the
+// full-warp mask here: on sm_100 the sub-warp forms (a vote, shuffle or redux
+// whose member mask names 8 lanes) cost several hundred cycles each, the
+// full-mask forms a few tens; the groups are carved out of the full-warp result
+// (shift + mask for votes, width-8 shuffles, an xor butterfly for the OR).
+__device__ __forceinline__ uint32_t group_or(uint32_t mine) {
+    mine |= __shfl_xor_sync(kFull, mine, 1);
+    mine |= __shfl_xor_sync(kFull, mine, 2);
+    mine |= __shfl_xor_sync(kFull, mine, 4);
+    return mine;
+}
+
 // XOR `mine` (a single bit, or 0) into the word that holds node n, combined
 // over the 8 lanes of a group.
 template <int W>
-__device__ __forceinline__ void flip_bits(uint32_t (&w)[W], unsigned gmask, uint32_t mine,
-                                          unsigned n) {
+__device__ __forceinline__ void flip_bits(uint32_t (&w)[W], uint32_t mine, unsigned n) {
     if constexpr (W == 1) {
-        w[0] ^= __reduce_or_sync(gmask, mine);
+        w[0] ^= group_or(mine);
     } else {
 #pragma unroll
         for (int i = 0; i < W; ++i)
-            w[i] ^= __reduce_or_sync(gmask, (n >> 5) == static_cast<unsigned>(i) ? mine : 0u);
+            w[i] ^= group_or((n >> 5) == static_cast<unsigned>(i) ? mine : 0u);
     }
 }
 
 struct GroupCtx {
     unsigned g;      // lane within the group = level handled
-    unsigned gmask;  // lanes of this group
     unsigned gshift; // first lane of this group
 };
 
@@ -146,10 +156,10 @@ __device__ __forceinline__ float group_sink(float *K, V *Vv, uint32_t (&sb)[W], 
     const V av = Vv[node - 1];
     const float sk = K[(has_sib ? (node ^ 1u) : node) - 1];
     // children strictly smaller than the moving key move up one level
-    const unsigned cm = __ballot_sync(c.gmask, on && a < k) >> c.gshift;
+    const unsigned cm = (__ballot_sync(kFull, on && a < k) >> c.gshift) & 0xffu;
     const unsigned cnt = __ffs(~cm) - 1;  // number of leading levels that move
-    const float a_next = __shfl_down_sync(c.gmask, a, 1, kGroup);
-    const float a_first = __shfl_sync(c.gmask, a, 0, kGroup);
+    const float a_next = __shfl_down_sync(kFull, a, 1, kGroup);
+    const float a_first = __shfl_sync(kFull, a, 0, kGroup);
     const bool moves = on && t <= cnt;
     if (moves) { K[(node >> 1) - 1] = a; Vv[(node >> 1) - 1] = av; }
     if (active && t == max(cnt, 1u)) {
@@ -164,10 +174,10 @@ __device__ __forceinline__ float group_sink(float *K, V *Vv, uint32_t (&sb)[W], 
     const unsigned parent = node >> 1;
     const bool upd = moves && sib_ok;
     const uint32_t s_flip = (right < left) != (bit_at<W>(sb, parent) != 0);
-    flip_bits<W>(sb, c.gmask, (upd && s_flip) ? (1u << (parent & 31u)) : 0u, parent);
+    flip_bits<W>(sb, (upd && s_flip) ? (1u << (parent & 31u)) : 0u, parent);
     if constexpr (kHasLb) {
         const uint32_t l_flip = (right > left) != (bit_at<W>(lb, parent) != 0);
-        flip_bits<W>(lb, c.gmask, (upd && l_flip) ? (1u << (parent & 31u)) : 0u, parent);
+        flip_bits<W>(lb, (upd && l_flip) ? (1u << (parent & 31u)) : 0u, parent);
     }
     __syncwarp();
     return cnt == 0 ? k : a_first;
@@ -192,7 +202,7 @@ __device__ __forceinline__ void group_replace_at(float *K, V *Vv, uint32_t (&sb)
     const V bv = Vv[node - 1];
     const float sk = K[(has_sib ? (child ^ 1u) : child) - 1];
     // ancestors strictly larger than the new key move down one level
-    const unsigned cm = __ballot_sync(c.gmask, on && b > k) >> c.gshift;
+    const unsigned cm = (__ballot_sync(kFull, on && b > k) >> c.gshift) & 0xffu;
     const unsigned s = cm ? (__ffs(cm) - 1) : L;  // level where the new element lands
     const bool moves = on && t >= s;
     if (moves) { K[child - 1] = b; Vv[child - 1] = bv; }
@@ -208,8 +218,8 @@ __device__ __forceinline__ void group_replace_at(float *K, V *Vv, uint32_t (&sb)
     const bool upd = on && t + 1u >= s && has_sib;
     const bool s_flip = (right < left) != (bit_at<W>(sb, node) != 0);
     const bool l_flip = (right > left) != (bit_at<W>(lb, node) != 0);
-    flip_bits<W>(sb, c.gmask, (upd && s_flip) ? (1u << (node & 31u)) : 0u, node);
-    flip_bits<W>(lb, c.gmask, (upd && l_flip) ? (1u << (node & 31u)) : 0u, node);
+    flip_bits<W>(sb, (upd && s_flip) ? (1u << (node & 31u)) : 0u, node);
+    flip_bits<W>(lb, (upd && l_flip) ? (1u << (node & 31u)) : 0u, node);
     __syncwarp();
 }
 
@@ -325,7 +335,7 @@ __device__ __forceinline__ int next_below(const float *cand_d, const GroupCtx &c
     while (__any_sync(kFull, searching)) {
         const int sc = s + static_cast<int>(c.g);
         const float dist = (searching && sc < count) ? cand_d[deal_index(sc, beam)] : CUDART_INF_F;
-        const unsigned m = __ballot_sync(c.gmask, dist < limit) >> c.gshift;
+        const unsigned m = (__ballot_sync(kFull, dist < limit) >> c.gshift) & 0xffu;
         if (searching) {
             if (m) { s += __ffs(m) - 1; searching = false; }
             else { s += kGroup; searching = s < count; }
@@ -360,7 +370,6 @@ traverse_kernel(Layout L, int64_t *__restrict__ out_I, float *__restrict__ out_D
     gc.g = lane & 7;
     const int beam = lane >> 3;  // heap this lane's group works on
     gc.gshift = beam * kGroup;
-    gc.gmask = 0xffu << gc.gshift;
 
     for (int i = threadIdx.x; i < kBloomWords; i += kThreads) bloom[i] = 0;
     for (int i = threadIdx.x; i < d; i += kThreads) q_s[i] = query[b * ldq + i];
