@@ -24,7 +24,6 @@ import json
 import os
 import statistics
 import sys
-import threading
 import time
 from pathlib import Path
 
@@ -94,68 +93,60 @@ def load_or_build(cfg: int, device, rank: int, world: int):
 # --------------------------------------------------------------------- clocks
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons of one GPU while the timed region runs."""
+    """Samples SM clock and throttle reasons of one GPU while the timed region
+    runs, in a separate nvidia-smi process (a sampling thread in this process
+    would contend for the interpreter lock with the launches being timed)."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, device_index: int):
-        self.idx = device_index
-        self.samples: list[int] = []
-        self.reasons: set[str] = set()
-        self.max_mhz = None
-        self._stop = threading.Event()
-        self._thread = None
-        try:
-            import pynvml
-            pynvml.nvmlInit()
-            self.nv = pynvml
-            uuid = torch.cuda.get_device_properties(device_index).uuid
-            self.h = None
-            for i in range(pynvml.nvmlDeviceGetCount()):
-                h = pynvml.nvmlDeviceGetHandleByIndex(i)
-                u = pynvml.nvmlDeviceGetUUID(h)
-                u = u.decode() if isinstance(u, bytes) else u
-                if str(uuid) in u:
-                    self.h = h
-            if self.h is None:
-                self.h = pynvml.nvmlDeviceGetHandleByIndex(device_index)
-            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
-        except Exception as exc:  # no NVML: report nulls
-            log(f"[bench] NVML unavailable: {exc}")
-            self.nv = None
-
-    def _run(self):
-        nv = self.nv
-        names = {
-            "hw_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
-            "hw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
-            "sw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
-            "sw_power_cap": getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4),
-        }
-        while not self._stop.is_set():
-            try:
-                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
-                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
-                for name, bit in names.items():
-                    if mask & bit:
-                        self.reasons.add(name)
-            except Exception:
-                pass
-            self._stop.wait(0.02)
+        self.uuid = str(torch.cuda.get_device_properties(device_index).uuid)
+        if not self.uuid.startswith("GPU-"):
+            self.uuid = "GPU-" + self.uuid
+        self.proc = None
+        self.lines: list[str] = []
 
     def __enter__(self):
-        if self.nv is not None:
-            self._thread = threading.Thread(target=self._run, daemon=True)
-            self._thread.start()
+        import subprocess
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", self.uuid, f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "50"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            time.sleep(0.3)           # let it take its first samples
+        except Exception as exc:
+            log(f"[bench] nvidia-smi unavailable: {exc}")
+            self.proc = None
         return self
 
     def __exit__(self, *exc):
-        self._stop.set()
-        if self._thread is not None:
-            self._thread.join()
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                out, _ = self.proc.communicate(timeout=5)
+                self.lines = [ln for ln in out.splitlines() if ln.strip()]
+            except Exception:
+                self.proc.kill()
 
     def summary(self):
-        return {"sm_mhz": statistics.median(self.samples) if self.samples else None,
-                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
-                "samples": len(self.samples)}
+        clocks, max_mhz, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [x.strip() for x in ln.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                clocks.append(int(parts[0])); max_mhz = int(parts[1])
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": max_mhz,
+                "reasons": sorted(reasons), "samples": len(clocks)}
 
 
 # ------------------------------------------------------------------ CPU legs
@@ -342,23 +333,28 @@ def main():
         torch.cuda.synchronize(device)
 
     # ---- value: inputs resident in HBM, CUDA events on the stage's stream ----
-    for _ in range(warmup):
-        flush_l2(flush)
-        torch.cuda.synchronize(device)
-        stage.search_device(q_dev, ef, out_I, out_D)
-        stage.synchronize()
-    launches0 = extension.launch_count()
+    # the clock sampler starts before the warm-up so that the GPU never idles
+    # between the warm-up and the timed steps
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
           for _ in range(steps)]
     sampler = ClockSampler(local)
-    barrier()
     with sampler:
+        for _ in range(warmup):
+            flush_l2(flush)
+            torch.cuda.synchronize(device)
+            stage.search_device(q_dev, ef, out_I, out_D)
+            stage.synchronize()
+        launches0 = extension.launch_count()
+        barrier()
         for a, b in ev:
             flush_l2(flush)
             torch.cuda.synchronize(device)
             a.record(stream)
             stage.search_device(q_dev, ef, out_I, out_D)
             b.record(stream)
+            # the next step's L2 flush runs on another stream: it must not start
+            # while this step's kernels are still running
+            torch.cuda.synchronize(device)
         barrier()
     launches = extension.launch_count() - launches0
     step_ms = [a.elapsed_time(b) for a, b in ev]
@@ -436,6 +432,7 @@ def main():
         "e2e": {"value": world * B * steps / (e2e_ms * 1e-3), "unit": "queries/s",
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": launches,
+        "step_ms": {"min": min(step_ms), "median": statistics.median(step_ms), "max": max(step_ms)},
         "clocks": sampler.summary(),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "peak_source": peak_src,

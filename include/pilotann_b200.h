@@ -101,6 +101,17 @@ int pa_route(int64_t *router, float *leaf_D, int64_t *leaf_I, const float *query
              const float *entry_vectors, int64_t batch, int d_model,
              int n_routers, int n_leaves, void *stream);
 
+/* Same result as pa_route, bit for bit, with the dense query x router part on the
+ * tensor cores (tcgen05, fp32-grade three-product TF32): the tensor-core scores
+ * shortlist the routers, the shortlisted ones are re-measured exactly.
+ * workspace: device memory of pa_route_workspace_floats(batch, n_routers) floats,
+ * 16-byte aligned; NULL falls back to pa_route. */
+int64_t pa_route_workspace_floats(int64_t batch, int n_routers);
+int pa_route_ws(int64_t *router, float *leaf_D, int64_t *leaf_I, const float *query,
+                const float *route_vectors, const int64_t *entry_nodes,
+                const float *entry_vectors, int64_t batch, int d_model, int n_routers,
+                int n_leaves, float *workspace, void *stream);
+
 /* ---- query projection ---------------------------------------------------
  * Replaces the CPU `query @ VT.T` of IndexStaged.search
  * (pilot_ann/layers/staged.py:198): out[b, j] = sum_k query[b,k] * VT[j,k] for
@@ -108,6 +119,11 @@ int pa_route(int64_t *router, float *leaf_D, int64_t *leaf_I, const float *query
  * [batch, ld_out] with ld_out >= d_out. */
 int pa_project(float *out, const float *query, const float *VT, int64_t batch,
                int d_model, int d_out, int64_t ld_out, void *stream);
+
+/* Synchronises the current device and returns 0, or 1 if a tensor-core kernel of
+ * this library gave up on a bounded wait since the last reset (its output is
+ * then undefined), or PA_ERR_CUDA.  No upstream counterpart. */
+int pa_device_status(int reset);
 
 /* ---- search stage object -------------------------------------------------
  * Replaces the GPU half of `pipeline` (extension/pipeline_cpu.cpp:32-145): its

@@ -20,7 +20,7 @@ SYMBOLS = (
     "pa_version", "pa_last_error", "pa_heap_size_for", "pa_traverse_csr", "pa_pack_graph",
     "pa_traverse_packed", "pa_route", "pa_project", "pa_stage_create", "pa_stage_destroy",
     "pa_stage_search", "pa_stage_search_device", "pa_stage_synchronize", "pa_stage_stream",
-    "pa_launch_count", "pa_search_reduced_noalloc",
+    "pa_launch_count", "pa_search_reduced_noalloc", "pa_device_status", "pa_route_ws", "pa_route_workspace_floats",
 )
 
 
@@ -57,6 +57,10 @@ def lib() -> ctypes.CDLL:
     L.pa_traverse_packed.argtypes = [P, P, P, P, P, P, P, P, c_int64, c_int64, c_int64,
                                      c_int, c_int, c_int, c_int, P, P]
     L.pa_route.argtypes = [P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int, P]
+    L.pa_route_ws.argtypes = [P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int, P, P]
+    L.pa_route_ws.restype = c_int
+    L.pa_route_workspace_floats.argtypes = [c_int64, c_int]
+    L.pa_route_workspace_floats.restype = c_int64
     L.pa_project.argtypes = [P, P, P, c_int64, c_int, c_int, c_int64, P]
     L.pa_stage_create.argtypes = [POINTER(P), POINTER(StageIndex), c_int64, c_int, c_int]
     L.pa_stage_destroy.argtypes = [P]
@@ -67,6 +71,8 @@ def lib() -> ctypes.CDLL:
     L.pa_stage_stream.argtypes = [P]
     L.pa_stage_stream.restype = P
     L.pa_launch_count.restype = c_int64
+    L.pa_device_status.argtypes = [c_int]
+    L.pa_device_status.restype = c_int
     L.pa_search_reduced_noalloc.argtypes = [P, P, P, P, P, P, P, P, P, c_int64, c_int64, c_int64,
                                             c_int, c_int, c_int, c_int, c_int, P]
     L.pa_search_reduced_noalloc.restype = c_int

@@ -91,7 +91,7 @@ extern "C" int pa_search_reduced_noalloc(
     float *entry_D = reinterpret_cast<float *>(scratch + kEntryElems * sizeof(int64_t));
     rc = route_launch(nullptr, entry_D, entry_I, query, d_principle, route_vectors, entry_nodes,
                       entry_vectors, batch, d_principle, route_vectors ? n_routers : 1, n_leaves,
-                      stream);
+                      nullptr, nullptr, stream);
     if (rc != PA_OK) return rc;
     return traverse_packed_launch(output_I, output_D, packed_nbr, row_of, storage, query,
                                   d_principle, entry_I, entry_D, batch, n_nodes, n_storage,

@@ -37,7 +37,11 @@ int traverse_packed_launch(int64_t *output_I, float *output_D, const int32_t *pa
 int route_launch(int64_t *router, float *leaf_D, int64_t *leaf_I, const float *query,
                  int64_t ldq, const float *route_vectors, const int64_t *entry_nodes,
                  const float *entry_vectors, int64_t batch, int d, int n_routers, int n_leaves,
-                 cudaStream_t stream);
+                 float *dots_ws, const float *rnorm2, cudaStream_t stream);
+int router_norms_launch(float *rnorm2, const float *route_vectors, int n_routers, int d,
+                        cudaStream_t stream);
+int gemm_tf32x3_launch(float *out, const float *A, const float *B, int M, int N, int K,
+                       int64_t lda, int64_t ldb, int64_t ldo, cudaStream_t stream);
 int project_launch(float *out, const float *query, const float *VT, int64_t batch, int d,
                    int d_out, int64_t ld_out, cudaStream_t stream);
 

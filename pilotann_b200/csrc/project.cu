@@ -2,6 +2,7 @@
 // pilot_ann/layers/staged.py:198).  out[b, j] = sum_k query[b, k] * VT[j, k].
 // Both operands are K-major, the natural "TN" contraction.
 #include "pa_common.cuh"
+#include "tc05.cuh"
 
 namespace pa {
 
@@ -51,9 +52,203 @@ project_kernel(float *__restrict__ out, const float *__restrict__ query,
     }
 }
 
+// ---- tensor-core path (tcgen05, TMEM accumulator) -----------------------------
+// out[m, n] = sum_k A[m, k] * B[n, k]; A, B fp32, both K-major.  fp32-grade
+// accuracy from TF32 tensor cores by the three-product split: x = big + small
+// with big = x truncated to TF32 and small = x - big (exact in fp32);
+// A.B ~= Abig.Bbig + Abig.Bsmall + Asmall.Bbig, all accumulated in one fp32
+// TMEM tile.  The split needs a register pass over the operands, so tiles are
+// staged global -> registers -> shared memory by the CTA's threads, written
+// directly in the 128-byte-swizzled K-major layout the tensor core reads; no
+// bulk-tensor (TMA) copy is involved.
+//
+// CTA tile 128 x 64, K slice 32 floats (one 128-byte swizzle row = four K=8
+// MMA steps), two stages.  Thread 0 issues the MMAs and commits them to the
+// stage's mbarrier; a stage is rewritten only after that barrier completed.
+// Epilogue: warps 0-3 read their 32 TMEM lanes with tcgen05.ld and store rows.
+namespace gemm {
+constexpr int BM = 128, BN = 64, BK = 32, STAGES = 2, THREADS = 256;
+constexpr int A_BYTES = BM * BK * 4, B_BYTES = BN * BK * 4;
+constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
+constexpr int DYN_SMEM = STAGES * STAGE_BYTES + 1024;
+constexpr uint32_t WAIT_LIMIT = 1u << 20;
+}  // namespace gemm
+
+__device__ int g_gemm_status = 0;  // 1 = a bounded wait ran out
+
+// element (row r, 16-byte chunk c) of a K-major tile with 128-byte swizzle
+__device__ __forceinline__ uint32_t sw128(uint32_t r, uint32_t c) {
+    return r * 128u + ((c ^ (r & 7u)) << 4);
+}
+
+__device__ __forceinline__ void split_store(uint32_t big_addr, uint32_t small_addr, float4 x) {
+    float4 b, s;
+    b.x = __uint_as_float(__float_as_uint(x.x) & 0xffffe000u);
+    b.y = __uint_as_float(__float_as_uint(x.y) & 0xffffe000u);
+    b.z = __uint_as_float(__float_as_uint(x.z) & 0xffffe000u);
+    b.w = __uint_as_float(__float_as_uint(x.w) & 0xffffe000u);
+    s.x = __fsub_rn(x.x, b.x); s.y = __fsub_rn(x.y, b.y);
+    s.z = __fsub_rn(x.z, b.z); s.w = __fsub_rn(x.w, b.w);
+    asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(big_addr), "f"(b.x), "f"(b.y),
+                 "f"(b.z), "f"(b.w) : "memory");
+    asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(small_addr), "f"(s.x), "f"(s.y),
+                 "f"(s.z), "f"(s.w) : "memory");
+}
+
+__global__ void __launch_bounds__(gemm::THREADS, 1)
+gemm_tf32x3_kernel(float *__restrict__ out, const float *__restrict__ A,
+                   const float *__restrict__ B, int M, int N, int K, int64_t lda, int64_t ldb,
+                   int64_t ldo) {
+    using namespace gemm;
+    extern __shared__ uint8_t dyn_smem[];
+    __shared__ __align__(8) uint64_t bars[STAGES];
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_s;
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t tiles = (tc05::smem_u32(dyn_smem) + 1023u) & ~1023u;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) tc05::mbar_init(tc05::smem_u32(&bars[s]), 1);
+        abort_s = 0;
+        tc05::fence_barrier_init();
+    }
+    if (warp == 0) tc05::tmem_alloc(tc05::smem_u32(&tmem_slot), BN);
+    tc05::fence_before_sync();
+    __syncthreads();
+    tc05::fence_after_sync();
+    const uint32_t tmem = tmem_slot;
+    constexpr uint32_t idesc = tc05::idesc_tf32(BM, BN);
+
+    const int nkb = (K + BK - 1) / BK;
+    bool aborted = false;
+    for (int kb = 0; kb < nkb; ++kb) {
+        const int s = kb % STAGES, use = kb / STAGES;
+        const int k0 = kb * BK;
+        // operands of this K slice: global -> registers (all loads first)
+        float4 ra[4], rb[2];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t idx = tid + THREADS * i, r = idx >> 3, c = idx & 7;
+            const int m = m0 + r, k = k0 + 4 * c;
+            ra[i] = (m < M && k < K) ? __ldg(reinterpret_cast<const float4 *>(A + m * lda + k))
+                                     : make_float4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const uint32_t idx = tid + THREADS * i, r = idx >> 3, c = idx & 7;
+            const int n = n0 + r, k = k0 + 4 * c;
+            rb[i] = (n < N && k < K) ? __ldg(reinterpret_cast<const float4 *>(B + n * ldb + k))
+                                     : make_float4(0, 0, 0, 0);
+        }
+        // the stage may be rewritten once the MMAs of its previous use are done
+        if (use > 0 && !tc05::mbar_wait_bounded(tc05::smem_u32(&bars[s]), (use - 1) & 1, WAIT_LIMIT))
+            abort_s = 1;
+        const uint32_t a_big = tiles + s * STAGE_BYTES, a_small = a_big + A_BYTES;
+        const uint32_t b_big = a_small + A_BYTES, b_small = b_big + B_BYTES;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t idx = tid + THREADS * i, o = sw128(idx >> 3, idx & 7);
+            split_store(a_big + o, a_small + o, ra[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const uint32_t idx = tid + THREADS * i, o = sw128(idx >> 3, idx & 7);
+            split_store(b_big + o, b_small + o, rb[i]);
+        }
+        tc05::fence_proxy_async_smem();
+        __syncthreads();
+        if (abort_s) { aborted = true; break; }
+        if (tid == 0) {
+            tc05::fence_after_sync();
+#pragma unroll
+            for (int k8 = 0; k8 < BK / 8; ++k8) {
+                const uint64_t da_b = tc05::smem_desc_sw128(a_big + k8 * 32);
+                const uint64_t da_s = tc05::smem_desc_sw128(a_small + k8 * 32);
+                const uint64_t db_b = tc05::smem_desc_sw128(b_big + k8 * 32);
+                const uint64_t db_s = tc05::smem_desc_sw128(b_small + k8 * 32);
+                tc05::mma_tf32(tmem, da_s, db_b, idesc, (kb | k8) != 0);
+                tc05::mma_tf32(tmem, da_b, db_s, idesc, 1);
+                tc05::mma_tf32(tmem, da_b, db_b, idesc, 1);
+            }
+            tc05::mma_commit(tc05::smem_u32(&bars[s]));
+        }
+    }
+    // the last commit covers every MMA issued before it
+    if (nkb > 0) {
+        const int last = nkb - 1;
+        if (!aborted &&
+            !tc05::mbar_wait_bounded(tc05::smem_u32(&bars[last % STAGES]), (last / STAGES) & 1,
+                                     WAIT_LIMIT))
+            aborted = true;
+    }
+    tc05::fence_after_sync();
+    if (aborted) {
+        if (tid == 0) atomicExch(&g_gemm_status, 1);
+    } else if (warp < 4) {
+        const int m = m0 + 32 * warp + lane;
+        const bool vec = (ldo % 4 == 0) && ((reinterpret_cast<uintptr_t>(out) & 15u) == 0);
+#pragma unroll
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+            uint32_t r[32];
+            if (nkb > 0) {
+                tc05::tmem_ld_32x32(tmem + ((32u * warp) << 16) + c0, r);
+                tc05::tmem_ld_wait();
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) r[j] = 0;
+            }
+            if (m < M) {
+                float *dst = out + m * ldo + n0 + c0;
+                if (vec && n0 + c0 + 32 <= N) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4)
+                        *reinterpret_cast<float4 *>(dst + j) =
+                            make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                        __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (n0 + c0 + j < N) dst[j] = __uint_as_float(r[j]);
+                }
+            }
+        }
+    }
+    tc05::fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tc05::tmem_dealloc(tmem, BN);
+}
+
+static bool gemm_operands_ok(const float *A, const float *B, int K, int64_t lda, int64_t ldb) {
+    return K % 4 == 0 && lda % 4 == 0 && ldb % 4 == 0 && aligned16(A) && aligned16(B);
+}
+
+int gemm_tf32x3_launch(float *out, const float *A, const float *B, int M, int N, int K,
+                       int64_t lda, int64_t ldb, int64_t ldo, cudaStream_t stream) {
+    static bool configured[64] = {};
+    int dev = 0;
+    PA_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        PA_CUDA_TRY(cudaFuncSetAttribute(gemm_tf32x3_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         gemm::DYN_SMEM));
+        configured[dev] = true;
+    }
+    dim3 grid((N + gemm::BN - 1) / gemm::BN, (M + gemm::BM - 1) / gemm::BM);
+    gemm_tf32x3_kernel<<<grid, gemm::THREADS, gemm::DYN_SMEM, stream>>>(out, A, B, M, N, K, lda,
+                                                                        ldb, ldo);
+    count_launch();
+    PA_CUDA_TRY(cudaGetLastError());
+    return PA_OK;
+}
+
 int project_launch(float *out, const float *query, const float *VT, int64_t batch, int d,
                    int d_out, int64_t ld_out, cudaStream_t stream) {
     if (batch == 0 || d_out == 0) return PA_OK;
+    // tensor cores whenever the operands can be read as aligned float4 rows
+    if (gemm_operands_ok(query, VT, d, d, d))
+        return gemm_tf32x3_launch(out, query, VT, static_cast<int>(batch), d_out, d, d, d, ld_out,
+                                  stream);
     dim3 grid((d_out + kPT - 1) / kPT, static_cast<unsigned>((batch + kPT - 1) / kPT));
     project_kernel<<<grid, 256, 0, stream>>>(out, query, VT, batch, d, d_out, ld_out);
     count_launch();
@@ -72,4 +267,16 @@ extern "C" int pa_project(float *out, const float *query, const float *VT, int64
     PA_REQUIRE(out && query && VT, "null pointer");
     return project_launch(out, query, VT, batch, d_model, d_out, ld_out,
                           static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int pa_device_status(int reset) {
+    int status = 0;
+    if (cudaDeviceSynchronize() != cudaSuccess) return PA_ERR_CUDA;
+    if (cudaMemcpyFromSymbol(&status, pa::g_gemm_status, sizeof(int)) != cudaSuccess)
+        return PA_ERR_CUDA;
+    if (reset && status != 0) {
+        const int zero = 0;
+        cudaMemcpyToSymbol(pa::g_gemm_status, &zero, sizeof(int));
+    }
+    return status;
 }

@@ -22,6 +22,8 @@ struct pa_stage {
     int64_t *d_router = nullptr; // [max_batch]
     float *d_ep_D = nullptr;     // [max_batch, n_leaves]
     int64_t *d_ep_I = nullptr;   // [max_batch, n_leaves]
+    float *d_dots = nullptr;     // [max_batch, n_routers] tensor-core router scores
+    float *d_rnorm = nullptr;    // [n_routers] squared router norms
     int64_t *d_out_I = nullptr;  // [max_batch, 4, max_ef]
     float *d_out_D = nullptr;
 };
@@ -48,7 +50,7 @@ struct DeviceScope {
 // project (if the index has a rotation) -> route -> traverse for rows
 // [0, n) of the given buffers, all on one stream.
 static int enqueue_chunk(pa_stage *st, const float *raw, float *rot, int64_t *router,
-                         float *ep_D, int64_t *ep_I, int64_t *out_I, float *out_D, int64_t n,
+                         float *dots, float *ep_D, int64_t *ep_I, int64_t *out_I, float *out_D, int64_t n,
                          int ef, int32_t *stats, cudaStream_t stream) {
     const pa_stage_index &ix = st->ix;
     const float *rotated = raw;
@@ -59,7 +61,8 @@ static int enqueue_chunk(pa_stage *st, const float *raw, float *rot, int64_t *ro
     }
     int rc = route_launch(router, ep_D, ep_I, rotated, ix.d_model, ix.route_vectors,
                           ix.entry_nodes, ix.entry_vectors, n, ix.d_principle,
-                          ix.route_vectors ? ix.n_routers : 1, ix.n_leaves, stream);
+                          ix.route_vectors ? ix.n_routers : 1, ix.n_leaves, dots, st->d_rnorm,
+                          stream);
     if (rc != PA_OK) return rc;
     return traverse_packed_launch(out_I, out_D, ix.packed_nbr, ix.row_of, ix.storage, rotated,
                                   ix.d_model, ep_I, ep_D, n, ix.n_nodes, ix.n_storage,
@@ -121,9 +124,20 @@ extern "C" int pa_stage_create(pa_stage **out, const pa_stage_index *index, int6
     PA_STAGE_ALLOC(st->d_router, B * sizeof(int64_t));
     PA_STAGE_ALLOC(st->d_ep_D, B * ix.n_leaves * sizeof(float));
     PA_STAGE_ALLOC(st->d_ep_I, B * ix.n_leaves * sizeof(int64_t));
+    if (ix.route_vectors != nullptr && ix.n_routers > 1) {
+        PA_STAGE_ALLOC(st->d_dots, B * ix.n_routers * sizeof(float));
+        PA_STAGE_ALLOC(st->d_rnorm, ix.n_routers * sizeof(float));
+    }
     PA_STAGE_ALLOC(st->d_out_I, out_elems * sizeof(int64_t));
     PA_STAGE_ALLOC(st->d_out_D, out_elems * sizeof(float));
 #undef PA_STAGE_ALLOC
+    if (st->d_rnorm != nullptr) {
+        int rc = router_norms_launch(st->d_rnorm, ix.route_vectors, ix.n_routers, ix.d_principle,
+                                     st->streams[0]);
+        if (rc != PA_OK) { pa_stage_destroy(st); return rc; }
+        if ((e = cudaStreamSynchronize(st->streams[0])) != cudaSuccess)
+            return bail(e, "cudaStreamSynchronize");
+    }
     *out = st;
     return PA_OK;
 }
@@ -141,6 +155,8 @@ extern "C" void pa_stage_destroy(pa_stage *st) {
     cudaFree(st->d_router);
     cudaFree(st->d_ep_D);
     cudaFree(st->d_ep_I);
+    cudaFree(st->d_dots);
+    cudaFree(st->d_rnorm);
     cudaFree(st->d_out_I);
     cudaFree(st->d_out_D);
     delete st;
@@ -168,7 +184,9 @@ extern "C" int pa_stage_search(pa_stage *st, const float *host_query, float *hos
         float *rot = st->d_rot ? st->d_rot + lo * d : nullptr;
         PA_CUDA_TRY(cudaMemcpyAsync(raw, host_query + lo * d, sizeof(float) * m * d,
                                     cudaMemcpyHostToDevice, s));
-        rc = enqueue_chunk(st, raw, rot, st->d_router + lo, st->d_ep_D + lo * ix.n_leaves,
+        rc = enqueue_chunk(st, raw, rot, st->d_router + lo,
+                           st->d_dots ? st->d_dots + lo * ix.n_routers : nullptr,
+                           st->d_ep_D + lo * ix.n_leaves,
                            st->d_ep_I + lo * ix.n_leaves, st->d_out_I + lo * out_row,
                            st->d_out_D + lo * out_row, m, ef, nullptr, s);
         if (rc != PA_OK) return rc;
@@ -193,7 +211,8 @@ extern "C" int pa_stage_search_device(pa_stage *st, const float *dev_query, int6
     PA_REQUIRE(dev_query && dev_out_I && dev_out_D, "null device pointer");
     DeviceScope scope;
     PA_CUDA_TRY(scope.enter(st->device));
-    return enqueue_chunk(st, dev_query, st->d_rot, st->d_router, st->d_ep_D, st->d_ep_I,
+    return enqueue_chunk(st, dev_query, st->d_rot, st->d_router, st->d_dots, st->d_ep_D,
+                         st->d_ep_I,
                          dev_out_I, dev_out_D, batch, ef, dev_stats, st->streams[0]);
 }
 

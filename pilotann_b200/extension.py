@@ -133,11 +133,15 @@ def routing_cuda(query, route_vectors, entry_nodes, entry_vectors, with_ids: boo
     router = torch.empty(batch, dtype=torch.int64, device=query.device)
     distances = torch.empty(batch, n_leaves, dtype=torch.float32, device=query.device)
     ids = torch.empty(batch, n_leaves, dtype=torch.int64, device=query.device) if with_ids else None
+    # scratch for the tensor-core router scores (torch's caching allocator: no
+    # device synchronisation)
+    ws = torch.empty(int(_C.lib().pa_route_workspace_floats(batch, n_routers)),
+                     dtype=torch.float32, device=query.device)
     with torch.cuda.device(query.device):
-        _C.check(_C.lib().pa_route(
+        _C.check(_C.lib().pa_route_ws(
             router.data_ptr(), distances.data_ptr(), 0 if ids is None else ids.data_ptr(),
             query.data_ptr(), route_vectors.data_ptr(), entry_nodes.data_ptr(),
-            entry_vectors.data_ptr(), batch, d_model, n_routers, n_leaves,
+            entry_vectors.data_ptr(), batch, d_model, n_routers, n_leaves, ws.data_ptr(),
             _stream(query.device)))
     return [router, distances, ids] if with_ids else [router, distances]
 

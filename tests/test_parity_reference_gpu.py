@@ -71,9 +71,12 @@ def test_traversal_vs_upstream_kernel(ref_ext, law, d, ratio, ef):
         print(f"{law} d={d} ef={ef} packed={packed}: identical top-{k} {same:.4f} "
               f"(upstream run-to-run mismatch {jitter:.4f})")
         assert 1.0 - same <= max(0.005, 1.25 * jitter + 0.01)
-        # a query whose top-k differs typically differs in about one of its k ids, so
-        # upstream's own run-to-run mismatch moves its recall by ~jitter / k
-        assert abs(_recall(o_top, truth) - _recall(t_top, truth)) <= 0.002 + jitter / k
+        # recall: never worse than upstream beyond +-0.002 (+ upstream's own noise: a
+        # query whose top-k differs typically differs in about one of its k ids).  It
+        # may be better by up to the mismatch rate: upstream's races insert some nodes
+        # twice, which costs it heap slots and recall; the fixed schedule does not.
+        delta = _recall(o_top, truth) - _recall(t_top, truth)
+        assert -(0.002 + jitter / k) <= delta <= 0.002 + jitter
         # distances of ids both sides report, within 1e-5 relative
         for b in range(0, len(t_top), 17):
             mine = dict(zip(ours[0][b].flatten().tolist(), ours[1][b].flatten().tolist()))
