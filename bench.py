@@ -40,12 +40,23 @@ TARGET_RECALL = 0.90
 # ef_search at which GPU stage + upstream CPU refinement reach recall@10 >= 0.90 on
 # the seeded workloads (re-measured by the CPU leg of every N=1 run, which reports
 # the recall it sees at this ef)
-OPERATING_EF = {1: 16, 2: 16, 3: 128}
+OPERATING_EF = {1: 32, 2: 128, 3: 128}
 # ncu dram__bytes_read.sum + dram__bytes_write.sum per traversal launch divided by
 # the queries in that launch (bytes / query), from the capture summarised under
 # profiles/; None until captured
 NCU_TRAFFIC_PER_QUERY = {}
 FALLBACK_HBM_GBS = 6650.0
+
+
+# The upstream module prints progress lines to the C-level stdout; keep stdout for
+# the one JSON line by pointing file descriptor 1 at stderr and writing the
+# result to a private duplicate of the original descriptor.
+_RESULT_FD = os.dup(1)
+os.dup2(2, 1)
+
+
+def emit(line: dict) -> None:
+    os.write(_RESULT_FD, (json.dumps(line) + "\n").encode())
 
 
 def log(*a):
@@ -311,7 +322,7 @@ def main():
                 "cpu_baseline": base,
                 "e2e": {"value": base["value"], "unit": "queries/s", "h2d_bytes_per_step": 0,
                         "d2h_bytes_per_step": 0}}
-        print(json.dumps(line))
+        emit(line)
         return 0
 
     from pilotann_b200 import extension
@@ -445,7 +456,7 @@ def main():
         line["cpu_baseline"] = cpu_baseline_leg(w, index, queries, truth, ef)
     if world > 1:
         torch.distributed.destroy_process_group()
-    print(json.dumps(line))
+    emit(line)
     return 0
 
 
