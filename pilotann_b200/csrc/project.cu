@@ -63,11 +63,12 @@ project_kernel(float *__restrict__ out, const float *__restrict__ query,
 // bulk-tensor (TMA) copy is involved.
 //
 // CTA tile 128 x 64, K slice 32 floats (one 128-byte swizzle row = four K=8
-// MMA steps), two stages.  Thread 0 issues the MMAs and commits them to the
+// MMA steps), three stages; the next slice's global loads are issued before the
+// current slice's MMAs so that their latency overlaps the tensor work.  Thread 0 issues the MMAs and commits them to the
 // stage's mbarrier; a stage is rewritten only after that barrier completed.
 // Epilogue: warps 0-3 read their 32 TMEM lanes with tcgen05.ld and store rows.
 namespace gemm {
-constexpr int BM = 128, BN = 64, BK = 32, STAGES = 2, THREADS = 256;
+constexpr int BM = 128, BN = 64, BK = 32, STAGES = 3, THREADS = 256;
 constexpr int A_BYTES = BM * BK * 4, B_BYTES = BN * BK * 4;
 constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
 constexpr int DYN_SMEM = STAGES * STAGE_BYTES + 1024;
@@ -122,11 +123,10 @@ gemm_tf32x3_kernel(float *__restrict__ out, const float *__restrict__ A,
 
     const int nkb = (K + BK - 1) / BK;
     bool aborted = false;
-    for (int kb = 0; kb < nkb; ++kb) {
-        const int s = kb % STAGES, use = kb / STAGES;
+    // operands of a K slice: global -> registers
+    float4 ra[4], rb[2];
+    auto load_slice = [&](int kb) {
         const int k0 = kb * BK;
-        // operands of this K slice: global -> registers (all loads first)
-        float4 ra[4], rb[2];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const uint32_t idx = tid + THREADS * i, r = idx >> 3, c = idx & 7;
@@ -141,6 +141,10 @@ gemm_tf32x3_kernel(float *__restrict__ out, const float *__restrict__ A,
             rb[i] = (n < N && k < K) ? __ldg(reinterpret_cast<const float4 *>(B + n * ldb + k))
                                      : make_float4(0, 0, 0, 0);
         }
+    };
+    if (nkb > 0) load_slice(0);
+    for (int kb = 0; kb < nkb; ++kb) {
+        const int s = kb % STAGES, use = kb / STAGES;
         // the stage may be rewritten once the MMAs of its previous use are done
         if (use > 0 && !tc05::mbar_wait_bounded(tc05::smem_u32(&bars[s]), (use - 1) & 1, WAIT_LIMIT))
             abort_s = 1;
@@ -159,6 +163,7 @@ gemm_tf32x3_kernel(float *__restrict__ out, const float *__restrict__ A,
         tc05::fence_proxy_async_smem();
         __syncthreads();
         if (abort_s) { aborted = true; break; }
+        if (kb + 1 < nkb) load_slice(kb + 1);  // in flight while this slice's MMAs run
         if (tid == 0) {
             tc05::fence_after_sync();
 #pragma unroll

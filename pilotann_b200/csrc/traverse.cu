@@ -309,6 +309,14 @@ __device__ __forceinline__ void bloom_insert(uint32_t *bloom, int32_t v) {
     }
 }
 
+// What the open warp publishes about a beam's popped node.
+struct PopSlot {
+    int32_t node, row;
+    int64_t lo;
+    int len;
+    bool fetch;
+};
+
 __device__ __forceinline__ void pair_sync() {  // warps 0 and 1 only
     asm volatile("bar.sync 1, 64;" ::: "memory");
 }
@@ -360,6 +368,9 @@ traverse_kernel(Layout L, int64_t *__restrict__ out_I, float *__restrict__ out_D
     __shared__ int2 slots[kBeams * n_nb];  // survivors {global id, storage row}
     __shared__ float cand_d[kBeams * n_nb];
     __shared__ int n_work_s;
+    __shared__ uint2 probe_s[kBeams * n_nb];  // packed bloom probes of a round's slots
+    __shared__ PopSlot pop_s[kBeams];
+    __shared__ unsigned again_s[2];
     __shared__ int stat_s[4];
     extern __shared__ __align__(16) float q_s[];
 
@@ -380,6 +391,7 @@ traverse_kernel(Layout L, int64_t *__restrict__ out_I, float *__restrict__ out_D
         (&res_id[0][0])[i] = -1;
     }
     if (threadIdx.x < 4) stat_s[threadIdx.x] = 0;
+    if (threadIdx.x < 2) again_s[threadIdx.x] = 0;
     __syncthreads();
 
     float *okey = open_key[beam];
@@ -444,19 +456,21 @@ traverse_kernel(Layout L, int64_t *__restrict__ out_I, float *__restrict__ out_D
     // ---- rounds (traverse_cuda.cu:179-226) -----------------------------------------
     for (int step = 0; step < ef; ++step) {
         ++n_rounds;
-        if (w == 0) {
-            // pop until every beam holds a node with an adjacency row, or gives up
-            // (:118-134)
-            int2 e[kBeams][CH];
-            int32_t u_node = -1, u_row = -1;
-            int64_t u_lo = 0;
-            int u_len = 0;
-            const float bound = -rkey[0];
-            bool pending = true;
-            bool fetch = false;  // this beam's row must be (re)loaded
-            // every pop removes one element, so H + 1 pops always settle a beam; the
-            // guards only bound the loops should that invariant ever be broken
-            for (int outer = 0; outer <= H + 1; ++outer) {
+        // pop until every beam holds a node with an adjacency row, or gives up
+        // (:118-134).  Warp 0 pops; each warp then loads the neighbour row of "its"
+        // beam and prepares the bloom probes for it, so the four rows, their hashes
+        // and their elections proceed in parallel; warp 0 commits them in order.
+        int32_t u_node = -1, u_row = -1;   // warp 0: group-uniform per beam
+        int64_t u_lo = 0;
+        int u_len = 0;
+        bool pending = true;
+        for (int outer = 0; outer <= H + 1; ++outer) {  // more than one pass only if a
+                                                        // sampled node has an empty row
+            if (w == 0) {
+                const float bound = -rkey[0];
+                bool fetch = false;  // this beam's row must be (re)loaded
+                // every pop removes one element, so H + 1 pops always settle a beam;
+                // the guard only bounds the loop should that invariant ever be broken
                 for (int guard = 0; guard <= H + 1 && __any_sync(kFull, pending); ++guard) {
                     const float top_k = okey[0];
                     const int2 top_v = oval[0];
@@ -478,64 +492,78 @@ traverse_kernel(Layout L, int64_t *__restrict__ out_I, float *__restrict__ out_D
                         if (!pending) fetch = true;
                     }
                 }
-                // neighbour rows: lane i takes neighbour i (+32) of every beam
-                const unsigned fetch_any = __ballot_sync(kFull, fetch);
+                pending = false;
+                if (gc.g == 0) {
+                    pop_s[beam].node = u_node; pop_s[beam].row = u_row;
+                    pop_s[beam].lo = u_lo; pop_s[beam].len = u_len;
+                    pop_s[beam].fetch = fetch;
+                }
+                if (lane == 0) again_s[(outer + 1) & 1] = 0;
+            }
+            __syncthreads();
+            if (pop_s[w].fetch) {  // warp w serves beam w
+                const int32_t node_b = pop_s[w].node;
+                int2 e[CH];
+                if constexpr (Layout::kPacked) {
+                    const int32_t row_b = pop_s[w].row;
 #pragma unroll
-                for (int bb = 0; bb < kBeams; ++bb) {
-                    if (!((fetch_any >> (bb * kGroup)) & 1u)) continue;
-                    const int32_t node_b = __shfl_sync(kFull, u_node, bb * kGroup);
-                    if constexpr (Layout::kPacked) {
-                        const int32_t row_b = __shfl_sync(kFull, u_row, bb * kGroup);
+                    for (int c = 0; c < CH; ++c)
+                        e[c] = node_b >= 0
+                            ? __ldg(L.nbr + static_cast<int64_t>(row_b) * n_nb + 32 * c + lane)
+                            : make_int2(-1, -1);
+                } else {
+                    const int64_t lo_b = pop_s[w].lo;
+                    const int len_b = pop_s[w].len;
 #pragma unroll
-                        for (int c = 0; c < CH; ++c)
-                            e[bb][c] = node_b >= 0
-                                ? __ldg(L.nbr + static_cast<int64_t>(row_b) * n_nb + 32 * c + lane)
-                                : make_int2(-1, -1);
-                    } else {
-                        const int64_t lo_b = __shfl_sync(kFull, u_lo, bb * kGroup);
-                        const int len_b = __shfl_sync(kFull, u_len, bb * kGroup);
-#pragma unroll
-                        for (int c = 0; c < CH; ++c) {
-                            const int i = 32 * c + lane;
-                            e[bb][c] = (node_b >= 0 && i < len_b)
-                                ? make_int2(static_cast<int32_t>(__ldg(L.indices + lo_b + i)), -1)
-                                : make_int2(-1, -1);
-                        }
+                    for (int c = 0; c < CH; ++c) {
+                        const int i = 32 * c + lane;
+                        e[c] = (node_b >= 0 && i < len_b)
+                            ? make_int2(static_cast<int32_t>(__ldg(L.indices + lo_b + i)), -1)
+                            : make_int2(-1, -1);
                     }
                 }
-                fetch = false;
-                if constexpr (Layout::kPacked) {
-                    // a sampled node whose adjacency row is empty: pop again
-#pragma unroll
-                    for (int bb = 0; bb < kBeams; ++bb) {
-                        const int tag = __shfl_sync(kFull, e[bb][0].x, 0);
-                        if (bb == beam && u_node >= 0 && tag == kEmptyRowTag) {
-                            pending = true; u_node = -1;
-                        }
-                    }
-                    if (!__any_sync(kFull, pending)) break;
+                // a sampled node whose adjacency row is empty: its beam pops again
+                const bool empty_row = Layout::kPacked && node_b >= 0 &&
+                                       __shfl_sync(kFull, e[0].x, 0) == kEmptyRowTag;
+                if (empty_row) {
+                    if (lane == 0) atomicOr(&again_s[outer & 1], 1u << w);
                 } else {
-                    break;
+#pragma unroll
+                    for (int c = 0; c < CH; ++c) {
+                        const BloomProbe pr = bloom_prepare(e[c].x, lane);
+                        const int idx = w * n_nb + 32 * c + lane;
+                        slots[idx] = e[c];
+                        probe_s[idx] = make_uint2(
+                            pr.pos[0] | (pr.pos[1] << 15) | ((pr.elected & 3u) << 30),
+                            pr.pos[2] | (pr.pos[3] << 15) | ((pr.elected >> 2) << 30));
+                    }
                 }
             }
+            __syncthreads();
+            const unsigned again = again_s[outer & 1];
+            if (again == 0) break;
+            if (w == 0 && ((again >> beam) & 1u)) { pending = true; u_node = -1; }
+        }
+        if (w == 0) {
             n_expand += __popc(__ballot_sync(kFull, gc.g == 0 && u_node >= 0));
-
-            // bloom test-and-set in slot order, then compaction (:137-171).  Hashes and
-            // the same-bit elections of a chunk do not depend on the filter's state, so
-            // they are computed before the serial chain of atomics.
+            // bloom test-and-set in slot order, then compaction in place (:137-171):
+            // a chunk is read into registers before survivors are written, and
+            // survivors always land at or below the chunk's own position
             int off = 0;
-            BloomProbe probe[kBeams][CH];
-#pragma unroll
-            for (int bb = 0; bb < kBeams; ++bb)
-#pragma unroll
-                for (int c = 0; c < CH; ++c) probe[bb][c] = bloom_prepare(e[bb][c].x, lane);
 #pragma unroll
             for (int bb = 0; bb < kBeams; ++bb) {
 #pragma unroll
                 for (int c = 0; c < CH; ++c) {
-                    const bool seen = bloom_commit(bloom, probe[bb][c]);
+                    const int idx = bb * n_nb + 32 * c + lane;
+                    const int2 e = slots[idx];
+                    const uint2 pw = probe_s[idx];
+                    BloomProbe pr;
+                    pr.pos[0] = pw.x & 0x7fffu; pr.pos[1] = (pw.x >> 15) & 0x7fffu;
+                    pr.pos[2] = pw.y & 0x7fffu; pr.pos[3] = (pw.y >> 15) & 0x7fffu;
+                    pr.elected = (pw.x >> 30) | ((pw.y >> 30) << 2);
+                    const bool seen = bloom_commit(bloom, pr);
                     const unsigned m = __ballot_sync(kFull, !seen);
-                    if (!seen) slots[off + __popc(m & ((1u << lane) - 1u))] = e[bb][c];
+                    if (!seen) slots[off + __popc(m & ((1u << lane) - 1u))] = e;
                     off += __popc(m);
                 }
             }
