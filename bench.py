@@ -441,7 +441,7 @@ def main():
         "ms_per_step": total_ms / steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
         "e2e": {"value": world * B * steps / (e2e_ms * 1e-3), "unit": "queries/s",
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+                "h2d_bytes_per_step": world * h2d, "d2h_bytes_per_step": world * d2h},
         "gpu_launches": launches,
         "step_ms": {"min": min(step_ms), "median": statistics.median(step_ms), "max": max(step_ms)},
         "clocks": sampler.summary(),

@@ -1,6 +1,6 @@
 // Shared declarations of the sm_100a search-stage library: error plumbing,
-// the bloom hash and the three heap primitives whose exact semantics (element
-// layout included) decide which candidates a query keeps.
+// launchers shared between translation units, the constants with search
+// semantics and the bloom hash.
 #pragma once
 
 #include <cuda_runtime.h>
@@ -67,76 +67,6 @@ __host__ __device__ __forceinline__ uint32_t fnv1a_32(uint32_t x, uint32_t h) {
         h *= kFnvPrime;
     }
     return h;
-}
-
-// ---- heaps (upstream heapq.cuh:13-87) ---------------------------------------
-// Binary min-heaps over parallel key / value arrays.  V is whatever rides with
-// the key (an id, or an id + row pair).
-
-template <typename V>
-__device__ __forceinline__ void sift_root_down(float *keys, V *vals, int hsize) {
-    // heapq.cuh:13-29
-    int cursor = 0;
-    float ck = keys[0];
-    V cv = vals[0];
-    for (int child = 1; child < hsize; child = 2 * cursor + 1) {
-        int right = child + 1;
-        float k = keys[child];
-        if (right < hsize) {
-            float kr = keys[right];
-            if (kr < k) { child = right; k = kr; }
-        }
-        if (ck <= k) break;
-        keys[cursor] = k;
-        vals[cursor] = vals[child];
-        cursor = child;
-    }
-    keys[cursor] = ck;
-    vals[cursor] = cv;
-}
-
-template <typename V>
-__device__ __forceinline__ void heap_pop(float *keys, V *vals, int hsize, V empty,
-                                         float &out_key, V &out_val) {
-    // heapq.cuh:38-45
-    out_key = keys[0];
-    out_val = vals[0];
-    keys[0] = CUDART_INF_F;
-    vals[0] = empty;
-    sift_root_down(keys, vals, hsize);
-}
-
-template <typename V>
-__device__ __forceinline__ void heap_replace(float *keys, V *vals, int hsize, float k, V v) {
-    // heapq.cuh:47-77: walk to a leaf along the larger child (right only if
-    // strictly larger), give up if the new key is not smaller, else overwrite
-    // that leaf and sift up while the parent is strictly larger
-    int cursor = 0;
-    for (int child = 1; child < hsize; child = 2 * cursor + 1) {
-        int right = child + 1;
-        if (right < hsize && keys[right] > keys[child]) child = right;
-        cursor = child;
-    }
-    if (k >= keys[cursor]) return;
-    while (cursor > 0) {
-        int parent = (cursor - 1) >> 1;
-        float pk = keys[parent];
-        if (pk <= k) break;
-        keys[cursor] = pk;
-        vals[cursor] = vals[parent];
-        cursor = parent;
-    }
-    keys[cursor] = k;
-    vals[cursor] = v;
-}
-
-template <typename V>
-__device__ __forceinline__ void heap_pushpop(float *keys, V *vals, int hsize, float k, V v) {
-    // heapq.cuh:79-87
-    if (k <= keys[0]) return;
-    keys[0] = k;
-    vals[0] = v;
-    sift_root_down(keys, vals, hsize);
 }
 
 }  // namespace pa

@@ -36,6 +36,10 @@ def router_init(storage: torch.Tensor, init_nodes: list | None, n_routers: int,
     visited: set[int] = set()
     entry_nodes: list[list[int]] = [[] for _ in range(n_routers)]
     pool_size = min(1024, n_routers ** 2)
+    if n_storage < n_leaves * pool_size:
+        # upstream draws without this check and would spin forever
+        raise ValueError(f"router_init needs at least n_leaves * {pool_size} = "
+                         f"{n_leaves * pool_size} vectors, got {n_storage}")
     for _ in range(n_leaves):
         pool: list[int] = []
         seen_here: set[int] = set()
