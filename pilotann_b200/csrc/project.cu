@@ -1,6 +1,8 @@
 // Query projection: rotated = query @ VT^T (upstream runs this on the CPU,
 // pilot_ann/layers/staged.py:198).  out[b, j] = sum_k query[b, k] * VT[j, k].
 // Both operands are K-major, the natural "TN" contraction.
+#include <cuda.h>
+
 #include "pa_common.cuh"
 #include "tc05.cuh"
 
@@ -52,21 +54,22 @@ project_kernel(float *__restrict__ out, const float *__restrict__ query,
     }
 }
 
-// ---- tensor-core path (tcgen05, TMEM accumulator) -----------------------------
+// ---- tensor-core path (TMA -> shared memory -> tcgen05, TMEM accumulator) ------
 // out[m, n] = sum_k A[m, k] * B[n, k]; A, B fp32, both K-major.  fp32-grade
 // accuracy from TF32 tensor cores by the three-product split: x = big + small
 // with big = x truncated to TF32 and small = x - big (exact in fp32);
-// A.B ~= Abig.Bbig + Abig.Bsmall + Asmall.Bbig, all accumulated in one fp32
-// TMEM tile.  The split needs a register pass over the operands, so tiles are
-// staged global -> registers -> shared memory by the CTA's threads, written
-// directly in the 128-byte-swizzled K-major layout the tensor core reads; no
-// bulk-tensor (TMA) copy is involved.
+// A.B ~= Asmall.Bbig + Abig.Bsmall + Abig.Bbig, all accumulated in one fp32 TMEM
+// tile.
 //
-// CTA tile 128 x 64, K slice 32 floats (one 128-byte swizzle row = four K=8
-// MMA steps), three stages; the next slice's global loads are issued before the
-// current slice's MMAs so that their latency overlaps the tensor work.  Thread 0 issues the MMAs and commits them to the
-// stage's mbarrier; a stage is rewritten only after that barrier completed.
-// Epilogue: warps 0-3 read their 32 TMEM lanes with tcgen05.ld and store rows.
+// CTA tile 128 x 64, K slice 32 floats (one 128-byte swizzle row = four K=8 MMA
+// steps), three stages.  Per slice: thread 0 has a bulk-tensor (TMA) copy bring
+// the raw A and B tiles into the stage (SWIZZLE_128B, out-of-range rows and
+// columns zero-filled, completion on the stage's "full" mbarrier, prefetched two
+// slices ahead); all threads split the raw tile in place (raw -> big, small to a
+// second buffer; the transform is element-wise, so the swizzled layout is
+// untouched); thread 0 issues 12 MMAs and commits them to the stage's "empty"
+// mbarrier, after which the stage may be refilled.  Epilogue: warps 0-3 read
+// their 32 TMEM lanes with tcgen05.ld and store rows.  Every wait is bounded.
 namespace gemm {
 constexpr int BM = 128, BN = 64, BK = 32, STAGES = 3, THREADS = 256;
 constexpr int A_BYTES = BM * BK * 4, B_BYTES = BN * BK * 4;
@@ -77,13 +80,11 @@ constexpr uint32_t WAIT_LIMIT = 1u << 20;
 
 __device__ int g_gemm_status = 0;  // 1 = a bounded wait ran out
 
-// element (row r, 16-byte chunk c) of a K-major tile with 128-byte swizzle
-__device__ __forceinline__ uint32_t sw128(uint32_t r, uint32_t c) {
-    return r * 128u + ((c ^ (r & 7u)) << 4);
-}
-
-__device__ __forceinline__ void split_store(uint32_t big_addr, uint32_t small_addr, float4 x) {
-    float4 b, s;
+// raw fp32 chunk at `big_addr` -> TF32-exact part in place, remainder to `small_addr`
+__device__ __forceinline__ void split_in_place(uint32_t big_addr, uint32_t small_addr) {
+    float4 x, b, s;
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(x.x), "=f"(x.y), "=f"(x.z), "=f"(x.w) : "r"(big_addr) : "memory");
     b.x = __uint_as_float(__float_as_uint(x.x) & 0xffffe000u);
     b.y = __uint_as_float(__float_as_uint(x.y) & 0xffffe000u);
     b.z = __uint_as_float(__float_as_uint(x.z) & 0xffffe000u);
@@ -97,22 +98,37 @@ __device__ __forceinline__ void split_store(uint32_t big_addr, uint32_t small_ad
 }
 
 __global__ void __launch_bounds__(gemm::THREADS, 1)
-gemm_tf32x3_kernel(float *__restrict__ out, const float *__restrict__ A,
-                   const float *__restrict__ B, int M, int N, int K, int64_t lda, int64_t ldb,
-                   int64_t ldo) {
+gemm_tf32x3_kernel(float *__restrict__ out, const __grid_constant__ CUtensorMap map_a,
+                   const __grid_constant__ CUtensorMap map_b, int M, int N, int K, int64_t ldo) {
     using namespace gemm;
     extern __shared__ uint8_t dyn_smem[];
-    __shared__ __align__(8) uint64_t bars[STAGES];
+    __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES];
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_s;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t tiles = (tc05::smem_u32(dyn_smem) + 1023u) & ~1023u;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int nkb = (K + BK - 1) / BK;
+
+    auto stage_a = [&](int s) { return tiles + s * STAGE_BYTES; };
+    auto stage_b = [&](int s) { return tiles + s * STAGE_BYTES + 2 * A_BYTES; };
+    auto fill = [&](int kb) {  // thread 0: raw tiles of slice kb into its stage
+        const int s = kb % STAGES;
+        const uint32_t bar = tc05::smem_u32(&full_bar[s]);
+        tc05::mbar_expect_tx(bar, A_BYTES + B_BYTES);
+        tc05::tma_load_2d(stage_a(s), &map_a, kb * BK, m0, bar);
+        tc05::tma_load_2d(stage_b(s), &map_b, kb * BK, n0, bar);
+    };
 
     if (tid == 0) {
-        for (int s = 0; s < STAGES; ++s) tc05::mbar_init(tc05::smem_u32(&bars[s]), 1);
+        for (int s = 0; s < STAGES; ++s) {
+            tc05::mbar_init(tc05::smem_u32(&full_bar[s]), 1);
+            tc05::mbar_init(tc05::smem_u32(&empty_bar[s]), 1);
+        }
         abort_s = 0;
         tc05::fence_barrier_init();
+        tc05::tma_prefetch_desc(&map_a);
+        tc05::tma_prefetch_desc(&map_b);
     }
     if (warp == 0) tc05::tmem_alloc(tc05::smem_u32(&tmem_slot), BN);
     tc05::fence_before_sync();
@@ -121,49 +137,41 @@ gemm_tf32x3_kernel(float *__restrict__ out, const float *__restrict__ A,
     const uint32_t tmem = tmem_slot;
     constexpr uint32_t idesc = tc05::idesc_tf32(BM, BN);
 
-    const int nkb = (K + BK - 1) / BK;
+    if (tid == 0)
+        for (int kb = 0; kb < nkb && kb < STAGES - 1; ++kb) fill(kb);
+
     bool aborted = false;
-    // operands of a K slice: global -> registers
-    float4 ra[4], rb[2];
-    auto load_slice = [&](int kb) {
-        const int k0 = kb * BK;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const uint32_t idx = tid + THREADS * i, r = idx >> 3, c = idx & 7;
-            const int m = m0 + r, k = k0 + 4 * c;
-            ra[i] = (m < M && k < K) ? __ldg(reinterpret_cast<const float4 *>(A + m * lda + k))
-                                     : make_float4(0, 0, 0, 0);
-        }
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            const uint32_t idx = tid + THREADS * i, r = idx >> 3, c = idx & 7;
-            const int n = n0 + r, k = k0 + 4 * c;
-            rb[i] = (n < N && k < K) ? __ldg(reinterpret_cast<const float4 *>(B + n * ldb + k))
-                                     : make_float4(0, 0, 0, 0);
-        }
-    };
-    if (nkb > 0) load_slice(0);
     for (int kb = 0; kb < nkb; ++kb) {
         const int s = kb % STAGES, use = kb / STAGES;
-        // the stage may be rewritten once the MMAs of its previous use are done
-        if (use > 0 && !tc05::mbar_wait_bounded(tc05::smem_u32(&bars[s]), (use - 1) & 1, WAIT_LIMIT))
+        if (tid == 0) {
+            // refill the stage of the previous slice with the slice two ahead, once
+            // the MMAs that read it have completed
+            const int kn = kb + STAGES - 1;
+            if (kn < nkb) {
+                bool ok = true;
+                if (kn >= STAGES)
+                    ok = tc05::mbar_wait_bounded(tc05::smem_u32(&empty_bar[kn % STAGES]),
+                                                 ((kn / STAGES) - 1) & 1, WAIT_LIMIT);
+                if (ok) fill(kn); else abort_s = 1;
+            }
+        }
+        if (!tc05::mbar_wait_bounded(tc05::smem_u32(&full_bar[s]), use & 1, WAIT_LIMIT))
             abort_s = 1;
-        const uint32_t a_big = tiles + s * STAGE_BYTES, a_small = a_big + A_BYTES;
-        const uint32_t b_big = a_small + A_BYTES, b_small = b_big + B_BYTES;
+        const uint32_t a_big = stage_a(s), a_small = a_big + A_BYTES;
+        const uint32_t b_big = stage_b(s), b_small = b_big + B_BYTES;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const uint32_t idx = tid + THREADS * i, o = sw128(idx >> 3, idx & 7);
-            split_store(a_big + o, a_small + o, ra[i]);
+        for (int i = 0; i < A_BYTES / 16 / THREADS; ++i) {
+            const uint32_t o = (tid + THREADS * i) * 16u;
+            split_in_place(a_big + o, a_small + o);
         }
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            const uint32_t idx = tid + THREADS * i, o = sw128(idx >> 3, idx & 7);
-            split_store(b_big + o, b_small + o, rb[i]);
+        for (int i = 0; i < B_BYTES / 16 / THREADS; ++i) {
+            const uint32_t o = (tid + THREADS * i) * 16u;
+            split_in_place(b_big + o, b_small + o);
         }
         tc05::fence_proxy_async_smem();
         __syncthreads();
         if (abort_s) { aborted = true; break; }
-        if (kb + 1 < nkb) load_slice(kb + 1);  // in flight while this slice's MMAs run
         if (tid == 0) {
             tc05::fence_after_sync();
 #pragma unroll
@@ -176,15 +184,15 @@ gemm_tf32x3_kernel(float *__restrict__ out, const float *__restrict__ A,
                 tc05::mma_tf32(tmem, da_b, db_s, idesc, 1);
                 tc05::mma_tf32(tmem, da_b, db_b, idesc, 1);
             }
-            tc05::mma_commit(tc05::smem_u32(&bars[s]));
+            tc05::mma_commit(tc05::smem_u32(&empty_bar[s]));
         }
     }
     // the last commit covers every MMA issued before it
     if (nkb > 0) {
         const int last = nkb - 1;
         if (!aborted &&
-            !tc05::mbar_wait_bounded(tc05::smem_u32(&bars[last % STAGES]), (last / STAGES) & 1,
-                                     WAIT_LIMIT))
+            !tc05::mbar_wait_bounded(tc05::smem_u32(&empty_bar[last % STAGES]),
+                                     (last / STAGES) & 1, WAIT_LIMIT))
             aborted = true;
     }
     tc05::fence_after_sync();
@@ -228,6 +236,41 @@ static bool gemm_operands_ok(const float *A, const float *B, int K, int64_t lda,
     return K % 4 == 0 && lda % 4 == 0 && ldb % 4 == 0 && aligned16(A) && aligned16(B);
 }
 
+// cuTensorMapEncodeTiled, looked up through the runtime (no link against libcuda)
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+                cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// K-major fp32 matrix [rows, K] with row stride ld, tiles of box_rows x 32 floats
+static int make_tile_map(CUtensorMap *map, const float *base, int rows, int K, int64_t ld,
+                         int box_rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr) return fail(PA_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * sizeof(float)};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(gemm::BK), static_cast<cuuint32_t>(box_rows)};
+    const cuuint32_t elem[2] = {1, 1};
+    CUresult rc = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float *>(base), dims,
+                     strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS)
+        return fail(PA_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", static_cast<int>(rc));
+    return PA_OK;
+}
+
 int gemm_tf32x3_launch(float *out, const float *A, const float *B, int M, int N, int K,
                        int64_t lda, int64_t ldb, int64_t ldo, cudaStream_t stream) {
     static bool configured[64] = {};
@@ -239,9 +282,14 @@ int gemm_tf32x3_launch(float *out, const float *A, const float *B, int M, int N,
                                          gemm::DYN_SMEM));
         configured[dev] = true;
     }
+    CUtensorMap map_a, map_b;
+    int rc = make_tile_map(&map_a, A, M, K, lda, gemm::BM);
+    if (rc != PA_OK) return rc;
+    rc = make_tile_map(&map_b, B, N, K, ldb, gemm::BN);
+    if (rc != PA_OK) return rc;
     dim3 grid((N + gemm::BN - 1) / gemm::BN, (M + gemm::BM - 1) / gemm::BM);
-    gemm_tf32x3_kernel<<<grid, gemm::THREADS, gemm::DYN_SMEM, stream>>>(out, A, B, M, N, K, lda,
-                                                                        ldb, ldo);
+    gemm_tf32x3_kernel<<<grid, gemm::THREADS, gemm::DYN_SMEM, stream>>>(out, map_a, map_b, M, N, K,
+                                                                        ldo);
     count_launch();
     PA_CUDA_TRY(cudaGetLastError());
     return PA_OK;

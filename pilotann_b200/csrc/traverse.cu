@@ -12,12 +12,15 @@
 //     (__match_any_sync elects the first lane, the others see the bit as set);
 //   * each heap sees its operations in upstream's order.
 //
-// Work split inside the CTA (all four beams share every warp):
-//   warp 0  "open" warp: pops the four open heaps, fetches the four neighbour
-//           rows, runs the bloom filter and the compaction, and later applies
-//           heap_replace to the four open heaps;
+// Work split inside the CTA:
+//   warp 0  "open" warp: pops the four open heaps, commits the bloom probes in
+//           slot order, compacts the survivors, and later applies heap_replace
+//           to the four open heaps;
 //   warp 1  "result" warp: applies heap_pushpop to the four result heaps and
 //           writes the output;
+//   warp b  (every warp) loads the neighbour row of beam b and prepares its bloom
+//           probes (hashes and same-bit elections), so the four rows proceed in
+//           parallel;
 //   all warps: 16 teams of 8 lanes evaluate the distances of a round.
 // A heap operation is executed by a group of 8 lanes, one lane per level of the
 // root-to-leaf path, the four beams side by side in one warp.  The path is not

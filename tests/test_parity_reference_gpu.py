@@ -124,3 +124,36 @@ def test_golden_gpu_fixtures():
                                               r["entry_nodes"].cuda(), ev.cuda())
         assert torch.equal(router.cpu(), r["router"])
         assert torch.allclose(dist.cpu(), r["distances"], rtol=1e-5, atol=0.0)
+
+
+def test_pipeline_drop_in_vs_upstream_pipeline(ref_ext):
+    """kernels.pipeline of this package, fed upstream's own traverse_refine as the
+    consumer, against upstream's whole `pipeline` (extension/pipeline_cpu.cpp:32-145)
+    on the same tensors: same recall within +-0.005, exact distances, and mostly
+    the same ids (the GPU halves differ only through upstream's races)."""
+    from pilotann_b200 import kernels, utils
+    k, ef, chunk = 10, 64, 128
+    p = make_problem(n=20000, d=96, ratio=0.25, batch=512, n_init=64, seed=33, law="powerlaw",
+                     build_device="cuda")
+    full_indptr, full_indices = utils.graph_init(p["full"].cuda(), "nsw", 32)
+    c = to_cuda(p)
+    graph = [full_indptr, full_indices]
+    subgraph = [p["indptr"], p["indices"]]
+    sub_cuda = [c["indptr"], c["indices"], c["mapping"]]
+    d_p = 96      # no reduction in this test: the whole vector is "principal"
+    args = dict(storage=p["full"], storage_cuda=c["storage"], query=p["query"],
+                query_cuda=c["query"], initial_I=c["initial_I"], initial_D=c["initial_D"])
+    ours_I, ours_D = kernels.pipeline(graph=graph, subgraph=subgraph, subgraph_cuda=sub_cuda,
+                                      n_neighbors=32, k=k, ef_search=ef, d_principle=d_p,
+                                      chunk_size=chunk, refine=ref_ext.traverse_refine, **args)
+    theirs_I, theirs_D = ref_ext.pipeline(graph, subgraph, sub_cuda, args["storage"],
+                                          args["storage_cuda"], args["query"], args["query_cuda"],
+                                          args["initial_I"], args["initial_D"], 32, ef, d_p, k, chunk)
+    truth = utils.ground_truth(p["query"], p["full"], k)
+    r_ours, r_theirs = utils.recall(ours_I, truth), utils.recall(theirs_I, truth)
+    same = (ours_I.sort(dim=1).values == theirs_I.sort(dim=1).values).all(dim=1).float().mean()
+    print(f"pipeline recall ours {r_ours:.4f} upstream {r_theirs:.4f}, identical top-{k} {same:.4f}")
+    assert abs(r_ours - r_theirs) <= 0.005
+    assert same.item() >= 0.97
+    exact = torch.cdist(p["query"].unsqueeze(1), p["full"][ours_I]).squeeze(1).square()
+    assert torch.allclose(ours_D, exact, atol=1e-3)
