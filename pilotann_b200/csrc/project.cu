@@ -62,16 +62,20 @@ project_kernel(float *__restrict__ out, const float *__restrict__ query,
 // tile.
 //
 // CTA tile 128 x 64, K slice 32 floats (one 128-byte swizzle row = four K=8 MMA
-// steps), three stages.  Per slice: thread 0 has a bulk-tensor (TMA) copy bring
-// the raw A and B tiles into the stage (SWIZZLE_128B, out-of-range rows and
-// columns zero-filled, completion on the stage's "full" mbarrier, prefetched two
-// slices ahead); all threads split the raw tile in place (raw -> big, small to a
-// second buffer; the transform is element-wise, so the swizzled layout is
-// untouched); thread 0 issues 12 MMAs and commits them to the stage's "empty"
-// mbarrier, after which the stage may be refilled.  Epilogue: warps 0-3 read
-// their 32 TMEM lanes with tcgen05.ld and store rows.  Every wait is bounded.
+// steps), four stages, warp-specialised: a control thread keeps bulk-tensor
+// (TMA) copies of the raw A and B tiles three slices ahead (SWIZZLE_128B,
+// out-of-range rows and columns zero-filled, completion on the stage's "full"
+// mbarrier); eight converter warps split each raw tile in place (raw -> big,
+// small to a second buffer; the transform is element-wise, so the swizzled
+// layout is untouched) and arrive on the stage's "converted" mbarrier; the control
+// thread then issues the 12 MMAs of the slice and commits them to the stage's
+// "empty" mbarrier, after which the stage may be refilled.  No CTA-wide barrier
+// inside the K loop.  Epilogue: warps 0-3 read their 32 TMEM lanes with
+// tcgen05.ld and store rows.  Every wait is bounded.
 namespace gemm {
-constexpr int BM = 128, BN = 64, BK = 32, STAGES = 3, THREADS = 256;
+constexpr int BM = 128, BN = 64, BK = 32, STAGES = 4;
+constexpr int CONVERTERS = 256;           // threads that split the raw tiles
+constexpr int THREADS = CONVERTERS + 32;  // + one warp whose lane 0 drives TMA and MMA
 constexpr int A_BYTES = BM * BK * 4, B_BYTES = BN * BK * 4;
 constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
 constexpr int DYN_SMEM = STAGES * STAGE_BYTES + 1024;
@@ -102,9 +106,9 @@ gemm_tf32x3_kernel(float *__restrict__ out, const __grid_constant__ CUtensorMap 
                    const __grid_constant__ CUtensorMap map_b, int M, int N, int K, int64_t ldo) {
     using namespace gemm;
     extern __shared__ uint8_t dyn_smem[];
-    __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES];
+    __shared__ __align__(8) uint64_t full_bar[STAGES], conv_bar[STAGES], empty_bar[STAGES];
     __shared__ uint32_t tmem_slot;
-    __shared__ int abort_s;
+    __shared__ volatile int abort_s;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t tiles = (tc05::smem_u32(dyn_smem) + 1023u) & ~1023u;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
@@ -112,23 +116,15 @@ gemm_tf32x3_kernel(float *__restrict__ out, const __grid_constant__ CUtensorMap 
 
     auto stage_a = [&](int s) { return tiles + s * STAGE_BYTES; };
     auto stage_b = [&](int s) { return tiles + s * STAGE_BYTES + 2 * A_BYTES; };
-    auto fill = [&](int kb) {  // thread 0: raw tiles of slice kb into its stage
-        const int s = kb % STAGES;
-        const uint32_t bar = tc05::smem_u32(&full_bar[s]);
-        tc05::mbar_expect_tx(bar, A_BYTES + B_BYTES);
-        tc05::tma_load_2d(stage_a(s), &map_a, kb * BK, m0, bar);
-        tc05::tma_load_2d(stage_b(s), &map_b, kb * BK, n0, bar);
-    };
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) {
             tc05::mbar_init(tc05::smem_u32(&full_bar[s]), 1);
+            tc05::mbar_init(tc05::smem_u32(&conv_bar[s]), CONVERTERS / 32);
             tc05::mbar_init(tc05::smem_u32(&empty_bar[s]), 1);
         }
         abort_s = 0;
         tc05::fence_barrier_init();
-        tc05::tma_prefetch_desc(&map_a);
-        tc05::tma_prefetch_desc(&map_b);
     }
     if (warp == 0) tc05::tmem_alloc(tc05::smem_u32(&tmem_slot), BN);
     tc05::fence_before_sync();
@@ -137,43 +133,39 @@ gemm_tf32x3_kernel(float *__restrict__ out, const __grid_constant__ CUtensorMap 
     const uint32_t tmem = tmem_slot;
     constexpr uint32_t idesc = tc05::idesc_tf32(BM, BN);
 
-    if (tid == 0)
+    if (tid == CONVERTERS) {
+        // ---- control thread: TMA producer and MMA issuer -----------------------
+        tc05::tma_prefetch_desc(&map_a);
+        tc05::tma_prefetch_desc(&map_b);
+        auto fill = [&](int kb) {  // raw tiles of slice kb into its stage
+            const int s = kb % STAGES;
+            const uint32_t bar = tc05::smem_u32(&full_bar[s]);
+            tc05::mbar_expect_tx(bar, A_BYTES + B_BYTES);
+            tc05::tma_load_2d(stage_a(s), &map_a, kb * BK, m0, bar);
+            tc05::tma_load_2d(stage_b(s), &map_b, kb * BK, n0, bar);
+        };
         for (int kb = 0; kb < nkb && kb < STAGES - 1; ++kb) fill(kb);
-
-    bool aborted = false;
-    for (int kb = 0; kb < nkb; ++kb) {
-        const int s = kb % STAGES, use = kb / STAGES;
-        if (tid == 0) {
-            // refill the stage of the previous slice with the slice two ahead, once
-            // the MMAs that read it have completed
+        for (int kb = 0; kb < nkb && !abort_s; ++kb) {
+            const int s = kb % STAGES, use = kb / STAGES;
+            // keep the copies STAGES - 1 slices ahead: the stage to refill was read
+            // by the MMAs of slice kb - 1
             const int kn = kb + STAGES - 1;
             if (kn < nkb) {
-                bool ok = true;
-                if (kn >= STAGES)
-                    ok = tc05::mbar_wait_bounded(tc05::smem_u32(&empty_bar[kn % STAGES]),
-                                                 ((kn / STAGES) - 1) & 1, WAIT_LIMIT);
-                if (ok) fill(kn); else abort_s = 1;
+                if (kn >= STAGES &&
+                    !tc05::mbar_wait_bounded(tc05::smem_u32(&empty_bar[kn % STAGES]),
+                                             ((kn / STAGES) - 1) & 1, WAIT_LIMIT)) {
+                    abort_s = 1;
+                    break;
+                }
+                fill(kn);
             }
-        }
-        if (!tc05::mbar_wait_bounded(tc05::smem_u32(&full_bar[s]), use & 1, WAIT_LIMIT))
-            abort_s = 1;
-        const uint32_t a_big = stage_a(s), a_small = a_big + A_BYTES;
-        const uint32_t b_big = stage_b(s), b_small = b_big + B_BYTES;
-#pragma unroll
-        for (int i = 0; i < A_BYTES / 16 / THREADS; ++i) {
-            const uint32_t o = (tid + THREADS * i) * 16u;
-            split_in_place(a_big + o, a_small + o);
-        }
-#pragma unroll
-        for (int i = 0; i < B_BYTES / 16 / THREADS; ++i) {
-            const uint32_t o = (tid + THREADS * i) * 16u;
-            split_in_place(b_big + o, b_small + o);
-        }
-        tc05::fence_proxy_async_smem();
-        __syncthreads();
-        if (abort_s) { aborted = true; break; }
-        if (tid == 0) {
+            if (!tc05::mbar_wait_bounded(tc05::smem_u32(&conv_bar[s]), use & 1, WAIT_LIMIT)) {
+                abort_s = 1;
+                break;
+            }
             tc05::fence_after_sync();
+            const uint32_t a_big = stage_a(s), a_small = a_big + A_BYTES;
+            const uint32_t b_big = stage_b(s), b_small = b_big + B_BYTES;
 #pragma unroll
             for (int k8 = 0; k8 < BK / 8; ++k8) {
                 const uint64_t da_b = tc05::smem_desc_sw128(a_big + k8 * 32);
@@ -186,12 +178,36 @@ gemm_tf32x3_kernel(float *__restrict__ out, const __grid_constant__ CUtensorMap 
             }
             tc05::mma_commit(tc05::smem_u32(&empty_bar[s]));
         }
+    } else if (tid < CONVERTERS) {
+        // ---- converter warps: raw tile -> (big in place, small) ---------------
+        for (int kb = 0; kb < nkb && !abort_s; ++kb) {
+            const int s = kb % STAGES, use = kb / STAGES;
+            if (!tc05::mbar_wait_bounded(tc05::smem_u32(&full_bar[s]), use & 1, WAIT_LIMIT)) {
+                abort_s = 1;
+                break;
+            }
+            const uint32_t a_big = stage_a(s), a_small = a_big + A_BYTES;
+            const uint32_t b_big = stage_b(s), b_small = b_big + B_BYTES;
+#pragma unroll
+            for (int i = 0; i < A_BYTES / 16 / CONVERTERS; ++i) {
+                const uint32_t o = (tid + CONVERTERS * i) * 16u;
+                split_in_place(a_big + o, a_small + o);
+            }
+#pragma unroll
+            for (int i = 0; i < B_BYTES / 16 / CONVERTERS; ++i) {
+                const uint32_t o = (tid + CONVERTERS * i) * 16u;
+                split_in_place(b_big + o, b_small + o);
+            }
+            tc05::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) tc05::mbar_arrive(tc05::smem_u32(&conv_bar[s]));
+        }
     }
-    // the last commit covers every MMA issued before it
-    if (nkb > 0) {
+    // everyone: the last commit covers every MMA issued before it
+    bool aborted = abort_s != 0;
+    if (nkb > 0 && !aborted) {
         const int last = nkb - 1;
-        if (!aborted &&
-            !tc05::mbar_wait_bounded(tc05::smem_u32(&empty_bar[last % STAGES]),
+        if (!tc05::mbar_wait_bounded(tc05::smem_u32(&empty_bar[last % STAGES]),
                                      (last / STAGES) & 1, WAIT_LIMIT))
             aborted = true;
     }
