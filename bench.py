@@ -172,12 +172,19 @@ def load_reference():
 
 
 def omp_threads() -> int:
-    """Threads an OpenMP parallel region gets (what upstream's host code uses)."""
+    """Threads an OpenMP parallel region gets (what upstream's host code uses).
+    The CPU legs use every host core: launchers such as torchrun export
+    OMP_NUM_THREADS=1 to their workers, which would otherwise throttle the
+    baseline to one thread."""
     import ctypes
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
     try:
-        return int(ctypes.CDLL("libgomp.so.1").omp_get_max_threads())
+        gomp = ctypes.CDLL("libgomp.so.1")
+        gomp.omp_set_num_threads(n)
+        torch.set_num_threads(n)
+        return int(gomp.omp_get_max_threads())
     except Exception:
-        return os.cpu_count() or 1
+        return n
 
 
 def recall_at(I: torch.Tensor, truth: torch.Tensor, k: int) -> float:
