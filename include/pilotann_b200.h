@@ -66,8 +66,13 @@ int pa_traverse_csr(int64_t *output_I, float *output_D, const int64_t *indptr,
 /* ---- packed device-resident index --------------------------------------
  * Counterpart of the device copies `IndexStaged.to` prepares
  * (pilot_ann/layers/staged.py:124-139), laid out for one dependent load per
- * hop: packed_nbr [n_storage, n_neighbors] of int32 pairs {global id, storage
- * row} indexed by storage row, and row_of [n_nodes] int32 (= mapping).
+ * hop: packed_nbr [n_storage, n_neighbors][4] int32, indexed by storage row --
+ * per neighbour slot {global id, storage row, two words of bloom probes: the
+ * four 15-bit hash positions of the id (upstream bloom.cuh:9-16 chained as in
+ * traverse_cuda.cu:60-74) and, per hash step, whether the slot is the first of
+ * its 32-slot chunk to touch that bit} -- and row_of [n_nodes] int32
+ * (= mapping).  packed_nbr takes 16 * n_storage * n_neighbors bytes and must be
+ * 16-byte aligned.
  * Fails with PA_ERR_UNPACKABLE (after a stream synchronise) if a node with a
  * non-empty adjacency row has no storage row, or an id does not fit int32.
  * Synchronous. */

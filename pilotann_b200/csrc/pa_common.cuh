@@ -69,4 +69,51 @@ __host__ __device__ __forceinline__ uint32_t fnv1a_32(uint32_t x, uint32_t h) {
     return h;
 }
 
+// ---- bloom probes of a chunk of 32 neighbour slots -----------------------------
+// The filter is tested-and-set 32 slots at a time, the four hash steps in lock
+// step, and within a step lanes hitting the same bit are served in ascending
+// lane order: only the first ("elected") lane performs the atomic, the others
+// have a lower lane setting the very same bit in the same step and see it as
+// set.  Positions and elections depend on the 32 ids alone, so the packed index
+// stores them next to the ids; for upstream's CSR tensors they are computed on
+// the fly.
+struct BloomProbe {
+    uint32_t pos[kFnvSteps];
+    uint32_t elected;  // bit s: this lane performs the atomic of step s
+};
+
+#ifdef __CUDACC__
+// All 32 lanes of the warp call this together; v < 0 marks a slot without a node.
+__device__ __forceinline__ BloomProbe bloom_prepare(int32_t v, int lane) {
+    BloomProbe p;
+    const bool valid = v >= 0;
+    uint32_t h = kFnvOffset;
+    p.elected = 0;
+#pragma unroll
+    for (int s = 0; s < kFnvSteps; ++s) {
+        h = fnv1a_32(static_cast<uint32_t>(v), h);
+        p.pos[s] = h & (kBloomBits - 1);
+        // lanes without a node get a key no node can have
+        const uint32_t key = valid ? p.pos[s] : (0x80000000u | lane);
+        const uint32_t peers = __match_any_sync(0xffffffffu, key);
+        if (valid && (peers & ((1u << lane) - 1u)) == 0) p.elected |= 1u << s;
+    }
+    return p;
+}
+#endif
+
+// Two words per probe: positions are 15 bits each, the election bits ride on top.
+__host__ __device__ __forceinline__ uint2 probe_pack(const BloomProbe &p) {
+    return make_uint2(p.pos[0] | (p.pos[1] << 15) | ((p.elected & 3u) << 30),
+                      p.pos[2] | (p.pos[3] << 15) | ((p.elected >> 2) << 30));
+}
+__host__ __device__ __forceinline__ BloomProbe probe_unpack(uint2 w) {
+    BloomProbe p;
+    p.pos[0] = w.x & 0x7fffu; p.pos[1] = (w.x >> 15) & 0x7fffu;
+    p.pos[2] = w.y & 0x7fffu; p.pos[3] = (w.y >> 15) & 0x7fffu;
+    p.elected = (w.x >> 30) | ((w.y >> 30) << 2);
+    return p;
+}
+static_assert(kBloomBits == (1u << 15), "probe_pack stores 15-bit positions");
+
 }  // namespace pa

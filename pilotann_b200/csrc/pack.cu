@@ -5,12 +5,12 @@
 
 namespace pa {
 
-__global__ void pack_fill_kernel(int2 *nbr, int64_t n_pairs, int n_nb) {
+__global__ void pack_fill_kernel(int4 *nbr, int64_t n_slots, int n_nb) {
     int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
-    if (i < n_pairs) nbr[i] = make_int2((i % n_nb) == 0 ? kEmptyRowTag : -1, -1);
+    if (i < n_slots) nbr[i] = make_int4((i % n_nb) == 0 ? kEmptyRowTag : -1, -1, 0, 0);
 }
 
-__global__ void pack_rows_kernel(int2 *__restrict__ nbr, int32_t *__restrict__ row_of,
+__global__ void pack_rows_kernel(int4 *__restrict__ nbr, int32_t *__restrict__ row_of,
                                  const int64_t *__restrict__ indptr,
                                  const int64_t *__restrict__ indices,
                                  const int64_t *__restrict__ mapping, int64_t n_nodes,
@@ -39,7 +39,11 @@ __global__ void pack_rows_kernel(int2 *__restrict__ nbr, int32_t *__restrict__ r
                 e = make_int2(static_cast<int32_t>(v), r < 0 ? -1 : static_cast<int32_t>(r));
             }
         }
-        nbr[row * n_nb + i] = e;
+        // the bloom probes of the slot: a chunk of 32 slots is what the search
+        // tests-and-sets together, so the elections are a property of the row
+        const uint2 probe = probe_pack(bloom_prepare(e.x, lane));
+        nbr[row * n_nb + i] = make_int4(e.x, e.y, static_cast<int>(probe.x),
+                                        static_cast<int>(probe.y));
     }
 }
 
@@ -54,20 +58,21 @@ extern "C" int pa_pack_graph(int32_t *packed_nbr, int32_t *row_of, const int64_t
     PA_REQUIRE(n_nodes >= 0 && n_nodes < 0x7fffffff && n_storage >= 0 && n_storage < 0x7fffffff,
                "ids must fit int32");
     PA_REQUIRE(packed_nbr && row_of && indptr && indices && mapping, "null pointer");
-    PA_REQUIRE((reinterpret_cast<uintptr_t>(packed_nbr) & 7u) == 0, "packed_nbr must be 8-byte aligned");
+    PA_REQUIRE((reinterpret_cast<uintptr_t>(packed_nbr) & 15u) == 0,
+               "packed_nbr must be 16-byte aligned");
     int *error = nullptr;
     PA_CUDA_TRY(cudaMallocAsync(&error, sizeof(int), stream));
     PA_CUDA_TRY(cudaMemsetAsync(error, 0, sizeof(int), stream));
-    const int64_t n_pairs = n_storage * n_neighbors;
-    if (n_pairs > 0) {
-        pack_fill_kernel<<<static_cast<unsigned>((n_pairs + 255) / 256), 256, 0, stream>>>(
-            reinterpret_cast<int2 *>(packed_nbr), n_pairs, n_neighbors);
+    const int64_t n_slots = n_storage * n_neighbors;
+    if (n_slots > 0) {
+        pack_fill_kernel<<<static_cast<unsigned>((n_slots + 255) / 256), 256, 0, stream>>>(
+            reinterpret_cast<int4 *>(packed_nbr), n_slots, n_neighbors);
         count_launch();
     }
     if (n_nodes > 0) {
         const int64_t threads = n_nodes * 32;
         pack_rows_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, stream>>>(
-            reinterpret_cast<int2 *>(packed_nbr), row_of, indptr, indices, mapping, n_nodes,
+            reinterpret_cast<int4 *>(packed_nbr), row_of, indptr, indices, mapping, n_nodes,
             n_storage, n_neighbors, error);
         count_launch();
     }

@@ -18,9 +18,9 @@
 //           to the four open heaps;
 //   warp 1  "result" warp: applies heap_pushpop to the four result heaps and
 //           writes the output;
-//   warp b  (every warp) loads the neighbour row of beam b and prepares its bloom
-//           probes (hashes and same-bit elections), so the four rows proceed in
-//           parallel;
+//   warp b  (every warp) loads the neighbour row of beam b together with its
+//           bloom probes (CSR layout: computes hashes and same-bit elections),
+//           so the four rows proceed in parallel;
 //   all warps: 16 teams of 8 lanes evaluate the distances of a round.
 // A heap operation is executed by a group of 8 lanes, one lane per level of the
 // root-to-leaf path, the four beams side by side in one warp.  The path is not
@@ -36,9 +36,12 @@
 // Two index layouts are served by the same kernel body:
 //   CsrLayout    -- upstream's tensors as they are (int64 indptr / indices /
 //                   mapping): four dependent loads per hop, kept for drop-in use;
-//   PackedLayout -- int32 {global id, storage row} neighbour pairs indexed by
-//                   storage row, the row carried through the open heap: two
-//                   dependent loads per hop (neighbour row, vector rows).
+//   PackedLayout -- 16 bytes per neighbour slot, indexed by storage row: int32
+//                   global id and storage row (the row is carried through the
+//                   open heap) plus the slot's bloom probes -- hash positions and
+//                   same-bit elections are properties of the row, so they are
+//                   computed when the index is packed: two dependent loads per
+//                   hop (neighbour row, vector rows) and no hashing in the loop.
 #include "pa_common.cuh"
 
 namespace pa {
@@ -54,7 +57,7 @@ struct CsrLayout {
 
 struct PackedLayout {
     static constexpr bool kPacked = true;
-    const int2 *nbr;        // [n_storage, n_nb] {global id, storage row}
+    const int4 *nbr;        // [n_storage, n_nb] {global id, storage row, bloom probe (2 words)}
     const int32_t *row_of;  // [n_nodes]
     const float *storage;
     int64_t n_nodes;
@@ -96,6 +99,8 @@ __device__ __forceinline__ uint32_t bit_at(const uint32_t (&w)[W], unsigned n) {
 // Leaf reached from the root by following the bits.
 template <int H, int W>
 __device__ __forceinline__ unsigned follow_bits(const uint32_t (&w)[W]) {
+    // two dependent instructions per level: a funnel shift (it takes the shift
+    // count modulo 32 by itself) and one logic op merging the bit into 2n
     unsigned n = 1;
 #pragma unroll
     for (int l = 0; l < HeapShape<H>::kLog - 1; ++l) {
@@ -103,7 +108,7 @@ __device__ __forceinline__ unsigned follow_bits(const uint32_t (&w)[W]) {
         if (l < 5) word = w[0];
         else if (l == 5) word = word_of<1, W>(w);
         else word = (n & 32u) ? word_of<3, W>(w) : word_of<2, W>(w);
-        n = 2u * n + ((word >> (n & 31u)) & 1u);
+        n = (n << 1) | (__funnelshift_r(word, 0u, n) & 1u);
     }
     return n == H / 2 ? static_cast<unsigned>(H) : n;  // node H/2 has one child only
 }
@@ -144,27 +149,50 @@ struct GroupCtx {
 
 // Puts (k, v) at the root and sinks it (upstream __heapify_up, heapq.cuh:13-29).
 // Used for heap_pushpop (after its root test) and heap_pop (k = +inf).
-// Returns the new root key (group-uniform; meaningful only for active groups).
-template <int H, int W, bool kHasLb, typename V>
-__device__ __forceinline__ float group_sink(float *K, V *Vv, uint32_t (&sb)[W], uint32_t (&lb)[W],
-                                            const GroupCtx &c, bool active, float k, V v) {
+// The operation comes in two halves so that a caller running many of them can
+// issue the loads of the next path while it still decides which key to insert:
+// sink_load reads what lies along the path the bits point to (it depends on the
+// heap only), sink_apply moves the keys and refreshes the bits.  sink_apply
+// returns the new root key (group-uniform; meaningful only for active groups).
+template <typename V> struct SinkPath {
+    unsigned node;  // this lane's node on the path (level g + 1), 2 if none
+    bool in;        // the path reaches this lane's level
+    float a, sk;    // key of the node, key of its sibling
+    V av;
+};
+
+template <int H, int W, typename V>
+__device__ __forceinline__ SinkPath<V> sink_load(const float *K, const V *Vv,
+                                                 const uint32_t (&sb)[W], const GroupCtx &c) {
+    SinkPath<V> p;
     const unsigned leaf = follow_bits<H, W>(sb);
     const unsigned L = 31u - __clz(leaf);
     const unsigned t = c.g + 1u;  // this lane's level on the path
-    const bool on = active && t <= L;
-    const unsigned node = on ? (leaf >> (L - t)) : 2u;
-    const bool has_sib = node < static_cast<unsigned>(H);  // node H has no sibling
-    const bool sib_ok = on && has_sib;
-    const float a = on ? K[node - 1] : CUDART_INF_F;
-    const V av = Vv[node - 1];
-    const float sk = K[(has_sib ? (node ^ 1u) : node) - 1];
+    p.in = t <= L;
+    p.node = p.in ? (leaf >> (L - t)) : 2u;
+    const bool has_sib = p.node < static_cast<unsigned>(H);  // node H has no sibling
+    p.a = K[p.node - 1];
+    p.av = Vv[p.node - 1];
+    p.sk = K[(has_sib ? (p.node ^ 1u) : p.node) - 1];
+    return p;
+}
+
+template <int H, int W, bool kHasLb, typename V>
+__device__ __forceinline__ float sink_apply(float *K, V *Vv, uint32_t (&sb)[W], uint32_t (&lb)[W],
+                                            const GroupCtx &c, const SinkPath<V> &p, bool active,
+                                            float k, V v) {
+    const unsigned t = c.g + 1u;  // this lane's level on the path
+    const unsigned node = p.node;
+    const bool on = active && p.in;
+    const bool sib_ok = on && node < static_cast<unsigned>(H);
+    const float a = on ? p.a : CUDART_INF_F;
     // children strictly smaller than the moving key move up one level
     const unsigned cm = (__ballot_sync(kFull, on && a < k) >> c.gshift) & 0xffu;
     const unsigned cnt = __ffs(~cm) - 1;  // number of leading levels that move
     const float a_next = __shfl_down_sync(kFull, a, 1, kGroup);
     const float a_first = __shfl_sync(kFull, a, 0, kGroup);
     const bool moves = on && t <= cnt;
-    if (moves) { K[(node >> 1) - 1] = a; Vv[(node >> 1) - 1] = av; }
+    if (moves) { K[(node >> 1) - 1] = a; Vv[(node >> 1) - 1] = p.av; }
     if (active && t == max(cnt, 1u)) {
         // cnt == 0: the new element stays at the root (written by level-1 lane)
         const unsigned at = cnt == 0 ? 1u : node;
@@ -173,7 +201,7 @@ __device__ __forceinline__ float group_sink(float *K, V *Vv, uint32_t (&sb)[W], 
     // refresh the bits of the parents of the moved nodes (path levels 0 .. cnt-1)
     const float nk = (t == cnt) ? k : a_next;  // new key at this lane's node
     const bool odd = node & 1u;
-    const float left = odd ? sk : nk, right = odd ? nk : sk;
+    const float left = odd ? p.sk : nk, right = odd ? nk : p.sk;
     const unsigned parent = node >> 1;
     const bool upd = moves && sib_ok;
     const uint32_t s_flip = (right < left) != (bit_at<W>(sb, parent) != 0);
@@ -186,29 +214,57 @@ __device__ __forceinline__ float group_sink(float *K, V *Vv, uint32_t (&sb)[W], 
     return cnt == 0 ? k : a_first;
 }
 
+template <int H, int W, bool kHasLb, typename V>
+__device__ __forceinline__ float group_sink(float *K, V *Vv, uint32_t (&sb)[W], uint32_t (&lb)[W],
+                                            const GroupCtx &c, bool active, float k, V v) {
+    const SinkPath<V> p = sink_load<H, W, V>(K, Vv, sb, c);
+    return sink_apply<H, W, kHasLb, V>(K, Vv, sb, lb, c, p, active, k, v);
+}
+
 // upstream heap_replace (heapq.cuh:47-77): walk to a leaf along the larger
 // child, give up if the new key is not smaller than that leaf, else overwrite it
-// and sift up while the parent is strictly larger.  group_replace_at is the
-// second half: `leaf` is the leaf the walk ends in and `accept` says whether
-// this group's key passed the test against it.
+// and sift up while the parent is strictly larger.  replace_load reads the
+// ancestors of `leaf` (the leaf the walk ends in) and the key of that leaf, the
+// acceptance limit; replace_apply is the second half, `accept` saying whether
+// this group's key passed the test against the limit.
+template <typename V> struct ReplacePath {
+    unsigned L, child;  // level of the leaf; this lane's path child (level g + 1), 2 if none
+    bool in;            // the path has an ancestor at this lane's level
+    float b, sk, limit; // ancestor key, key of the path child's sibling, key of the leaf
+    V bv;
+};
+
+template <int H, typename V>
+__device__ __forceinline__ ReplacePath<V> replace_load(const float *K, const V *Vv,
+                                                       const GroupCtx &c, unsigned leaf) {
+    ReplacePath<V> p;
+    p.L = 31u - __clz(leaf);
+    p.in = c.g < p.L;  // ancestors: levels 0 .. L-1
+    p.child = p.in ? (leaf >> (p.L - c.g - 1u)) : 2u;
+    const bool has_sib = p.child < static_cast<unsigned>(H);
+    p.b = K[(p.child >> 1) - 1];
+    p.bv = Vv[(p.child >> 1) - 1];
+    p.sk = K[(has_sib ? (p.child ^ 1u) : p.child) - 1];
+    p.limit = K[leaf - 1];
+    return p;
+}
+
 template <int H, int W, typename V>
-__device__ __forceinline__ void group_replace_at(float *K, V *Vv, uint32_t (&sb)[W],
-                                                 uint32_t (&lb)[W], const GroupCtx &c,
-                                                 unsigned leaf, bool accept, float k, V v) {
-    const unsigned L = 31u - __clz(leaf);
+__device__ __forceinline__ void replace_apply(float *K, V *Vv, uint32_t (&sb)[W],
+                                              uint32_t (&lb)[W], const GroupCtx &c, unsigned leaf,
+                                              const ReplacePath<V> &p, bool accept, float k, V v) {
+    const unsigned L = p.L;
     const unsigned t = c.g;  // ancestors: levels 0 .. L-1
-    const bool on = accept && t < L;
-    const unsigned child = on ? (leaf >> (L - t - 1u)) : 2u;
+    const bool on = accept && p.in;
+    const unsigned child = p.child;
     const unsigned node = child >> 1;
     const bool has_sib = child < static_cast<unsigned>(H);
-    const float b = K[node - 1];
-    const V bv = Vv[node - 1];
-    const float sk = K[(has_sib ? (child ^ 1u) : child) - 1];
+    const float b = p.b;
     // ancestors strictly larger than the new key move down one level
     const unsigned cm = (__ballot_sync(kFull, on && b > k) >> c.gshift) & 0xffu;
     const unsigned s = cm ? (__ffs(cm) - 1) : L;  // level where the new element lands
     const bool moves = on && t >= s;
-    if (moves) { K[child - 1] = b; Vv[child - 1] = bv; }
+    if (moves) { K[child - 1] = b; Vv[child - 1] = p.bv; }
     if (accept && t == min(s, L - 1u)) {
         // s == L: nothing moves, the new element replaces the leaf (level L-1 lane)
         const unsigned at = s == L ? leaf : node;
@@ -217,13 +273,21 @@ __device__ __forceinline__ void group_replace_at(float *K, V *Vv, uint32_t (&sb)
     // parents whose path child changed: levels max(s-1, 0) .. L-1
     const float nk = (t + 1u == s) ? k : b;  // new key of this lane's path child
     const bool odd = child & 1u;
-    const float left = odd ? sk : nk, right = odd ? nk : sk;
+    const float left = odd ? p.sk : nk, right = odd ? nk : p.sk;
     const bool upd = on && t + 1u >= s && has_sib;
     const bool s_flip = (right < left) != (bit_at<W>(sb, node) != 0);
     const bool l_flip = (right > left) != (bit_at<W>(lb, node) != 0);
     flip_bits<W>(sb, (upd && s_flip) ? (1u << (node & 31u)) : 0u, node);
     flip_bits<W>(lb, (upd && l_flip) ? (1u << (node & 31u)) : 0u, node);
     __syncwarp();
+}
+
+template <int H, int W, typename V>
+__device__ __forceinline__ void group_replace_at(float *K, V *Vv, uint32_t (&sb)[W],
+                                                 uint32_t (&lb)[W], const GroupCtx &c,
+                                                 unsigned leaf, bool accept, float k, V v) {
+    const ReplacePath<V> p = replace_load<H, V>(K, Vv, c, leaf);
+    replace_apply<H, W, V>(K, Vv, sb, lb, c, leaf, p, accept, k, v);
 }
 
 template <int H, int W, typename V>
@@ -236,10 +300,6 @@ __device__ __forceinline__ void group_replace(float *K, V *Vv, uint32_t (&sb)[W]
     group_replace_at<H, W>(K, Vv, sb, lb, c, leaf, accept, k, v);
 }
 
-// Next candidate of this group's beam, at or after position `s` of the beam's
-// list, whose distance is below `limit`; candidates are examined eight at a
-// time.  Returns the position (>= count if there is none).  Distances of
-// candidates that must not be inserted are stored as +inf.
 // ---- distance (upstream traverse_cuda.cu:18-43) -------------------------------
 // Eight lanes; lane t owns floats [32m + 4t, 32m + 4t + 4);
 // acc += fma(dx,dx,dy*dy); acc += fma(dz,dz,dw*dw); then the shuffle tree 4, 2, 1.
@@ -259,35 +319,14 @@ __device__ __forceinline__ float team_reduce(float acc) {
 
 // ---- bloom -----------------------------------------------------------------------
 // One chunk of 32 neighbours, test-and-set in the fixed order, in two parts.
-// bloom_prepare: the four bit positions of this lane's node and, per hash step,
-// whether this lane is the first (lowest) lane of the chunk that touches its bit
-// in that step.  bloom_commit: the serial part -- per step the elected lanes
+// The probes (bloom_prepare, or read from the packed index): the four bit
+// positions of this lane's node and, per hash step, whether this lane is the
+// first (lowest) lane of the chunk that touches its bit in that step.
+// bloom_commit: the serial part -- per step the elected lanes
 // atomically set their bit and learn whether it was set before; a lane that was
 // not elected has a lower lane setting the very same bit in the same step, so it
 // sees the bit as set.  Returns true for lanes whose node was already present
 // (or is not a node).
-struct BloomProbe {
-    uint32_t pos[kFnvSteps];
-    uint32_t elected;  // bit s: this lane performs the atomic of step s
-};
-
-__device__ __forceinline__ BloomProbe bloom_prepare(int32_t v, int lane) {
-    BloomProbe p;
-    const bool valid = v >= 0;
-    uint32_t h = kFnvOffset;
-    p.elected = 0;
-#pragma unroll
-    for (int s = 0; s < kFnvSteps; ++s) {
-        h = fnv1a_32(static_cast<uint32_t>(v), h);
-        p.pos[s] = h & (kBloomBits - 1);
-        // lanes without a node get a key no node can have
-        const uint32_t key = valid ? p.pos[s] : (0x80000000u | lane);
-        const uint32_t peers = __match_any_sync(kFull, key);
-        if (valid && (peers & ((1u << lane) - 1u)) == 0) p.elected |= 1u << s;
-    }
-    return p;
-}
-
 __device__ __forceinline__ bool bloom_commit(uint32_t *bloom, const BloomProbe &p) {
     bool found = true;
 #pragma unroll
@@ -353,6 +392,27 @@ __device__ __forceinline__ int next_below(const float *cand_d, const GroupCtx &c
         }
     }
     return s;
+}
+
+// The same search over a beam's list held in registers (lists of at most 32
+// candidates): lane g of the group holds the distances at positions g, g + 8,
+// g + 16 and g + 24 (+inf past the end).  Returns the positions whose distance
+// is below `limit` as a bit mask.
+__device__ __forceinline__ unsigned below_mask(const float (&cd)[4], float limit,
+                                               const GroupCtx &c) {
+    unsigned m = 0;
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+        m |= ((__ballot_sync(kFull, cd[k] < limit) >> c.gshift) & 0xffu) << (8 * k);
+    return m;
+}
+// Distance at position p of the list (p group-uniform).
+__device__ __forceinline__ float list_at(const float (&cd)[4], unsigned p) {
+    float mine = cd[0];
+    if ((p >> 3) == 1u) mine = cd[1];
+    if ((p >> 3) == 2u) mine = cd[2];
+    if ((p >> 3) == 3u) mine = cd[3];
+    return __shfl_sync(kFull, mine, p & 7u, kGroup);
 }
 
 template <int H, int CH, class Layout>
@@ -448,7 +508,7 @@ traverse_kernel(Layout L, int64_t *__restrict__ out_I, float *__restrict__ out_D
                 group_replace<H, W>(okey, oval, o_sb, o_lb, gc, have && e.x >= 0, dist, e);
             }
         } else if (w >= 2) {  // bloom: the union of the admitted entries' bits
-            for (int i = threadIdx.x - 64; i < n_here; i += kThreads - 64) {
+            for (int i = 32 * (w - 2) + lane; i < n_here; i += kThreads - 64) {
                 const int32_t node = slots[i].x;
                 if (node >= 0) bloom_insert(bloom, node);
             }
@@ -506,39 +566,38 @@ traverse_kernel(Layout L, int64_t *__restrict__ out_I, float *__restrict__ out_D
             __syncthreads();
             if (pop_s[w].fetch) {  // warp w serves beam w
                 const int32_t node_b = pop_s[w].node;
-                int2 e[CH];
                 if constexpr (Layout::kPacked) {
+                    // ids, rows and ready-made probes in one 16-byte load per lane
                     const int32_t row_b = pop_s[w].row;
+                    int4 e[CH];
 #pragma unroll
                     for (int c = 0; c < CH; ++c)
                         e[c] = node_b >= 0
                             ? __ldg(L.nbr + static_cast<int64_t>(row_b) * n_nb + 32 * c + lane)
-                            : make_int2(-1, -1);
+                            : make_int4(-1, -1, 0, 0);
+                    // a sampled node whose adjacency row is empty: its beam pops again
+                    if (node_b >= 0 && __shfl_sync(kFull, e[0].x, 0) == kEmptyRowTag) {
+                        if (lane == 0) atomicOr(&again_s[outer & 1], 1u << w);
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < CH; ++c) {
+                            const int idx = w * n_nb + 32 * c + lane;
+                            slots[idx] = make_int2(e[c].x, e[c].y);
+                            probe_s[idx] = make_uint2(static_cast<uint32_t>(e[c].z),
+                                                      static_cast<uint32_t>(e[c].w));
+                        }
+                    }
                 } else {
                     const int64_t lo_b = pop_s[w].lo;
                     const int len_b = pop_s[w].len;
 #pragma unroll
                     for (int c = 0; c < CH; ++c) {
                         const int i = 32 * c + lane;
-                        e[c] = (node_b >= 0 && i < len_b)
-                            ? make_int2(static_cast<int32_t>(__ldg(L.indices + lo_b + i)), -1)
-                            : make_int2(-1, -1);
-                    }
-                }
-                // a sampled node whose adjacency row is empty: its beam pops again
-                const bool empty_row = Layout::kPacked && node_b >= 0 &&
-                                       __shfl_sync(kFull, e[0].x, 0) == kEmptyRowTag;
-                if (empty_row) {
-                    if (lane == 0) atomicOr(&again_s[outer & 1], 1u << w);
-                } else {
-#pragma unroll
-                    for (int c = 0; c < CH; ++c) {
-                        const BloomProbe pr = bloom_prepare(e[c].x, lane);
-                        const int idx = w * n_nb + 32 * c + lane;
-                        slots[idx] = e[c];
-                        probe_s[idx] = make_uint2(
-                            pr.pos[0] | (pr.pos[1] << 15) | ((pr.elected & 3u) << 30),
-                            pr.pos[2] | (pr.pos[3] << 15) | ((pr.elected >> 2) << 30));
+                        const int32_t v = (node_b >= 0 && i < len_b)
+                            ? static_cast<int32_t>(__ldg(L.indices + lo_b + i)) : -1;
+                        const int idx = w * n_nb + i;
+                        slots[idx] = make_int2(v, -1);
+                        probe_s[idx] = probe_pack(bloom_prepare(v, lane));
                     }
                 }
             }
@@ -553,18 +612,44 @@ traverse_kernel(Layout L, int64_t *__restrict__ out_I, float *__restrict__ out_D
             // a chunk is read into registers before survivors are written, and
             // survivors always land at or below the chunk's own position
             int off = 0;
+            if constexpr (CH == 1) {
+                // all loads first, then the 16 atomics back to back, then the
+                // compaction: one exposed atomic latency instead of four
+                int2 ev[kBeams];
+                uint2 pv[kBeams];
+#pragma unroll
+                for (int bb = 0; bb < kBeams; ++bb) {
+                    ev[bb] = slots[bb * n_nb + lane];
+                    pv[bb] = probe_s[bb * n_nb + lane];
+                }
+                uint32_t miss[kBeams];  // nonzero: some probed bit was clear before
+#pragma unroll
+                for (int bb = 0; bb < kBeams; ++bb) {
+                    const BloomProbe pr = probe_unpack(pv[bb]);
+                    miss[bb] = 0;
+#pragma unroll
+                    for (int s = 0; s < kFnvSteps; ++s) {
+                        if ((pr.elected >> s) & 1u) {
+                            const uint32_t bit = 1u << (pr.pos[s] & 31);
+                            miss[bb] |= ~atomicOr(&bloom[pr.pos[s] >> 5], bit) & bit;
+                        }
+                        __syncwarp();
+                    }
+                }
+#pragma unroll
+                for (int bb = 0; bb < kBeams; ++bb) {
+                    const unsigned m = __ballot_sync(kFull, miss[bb] != 0);
+                    if (miss[bb] != 0) slots[off + __popc(m & ((1u << lane) - 1u))] = ev[bb];
+                    off += __popc(m);
+                }
+            } else
 #pragma unroll
             for (int bb = 0; bb < kBeams; ++bb) {
 #pragma unroll
                 for (int c = 0; c < CH; ++c) {
                     const int idx = bb * n_nb + 32 * c + lane;
                     const int2 e = slots[idx];
-                    const uint2 pw = probe_s[idx];
-                    BloomProbe pr;
-                    pr.pos[0] = pw.x & 0x7fffu; pr.pos[1] = (pw.x >> 15) & 0x7fffu;
-                    pr.pos[2] = pw.y & 0x7fffu; pr.pos[3] = (pw.y >> 15) & 0x7fffu;
-                    pr.elected = (pw.x >> 30) | ((pw.y >> 30) << 2);
-                    const bool seen = bloom_commit(bloom, pr);
+                    const bool seen = bloom_commit(bloom, probe_unpack(probe_s[idx]));
                     const unsigned m = __ballot_sync(kFull, !seen);
                     if (!seen) slots[off + __popc(m & ((1u << lane) - 1u))] = e;
                     off += __popc(m);
@@ -640,6 +725,46 @@ traverse_kernel(Layout L, int64_t *__restrict__ out_I, float *__restrict__ out_D
                 int valid = 0;
                 for (int j = lane; j < n_work; j += 32) valid += slots[j].y >= 0;
                 n_eval += __reduce_add_sync(kFull, valid);
+            }
+            if constexpr (CH == 1) {
+                // a beam's list has at most 32 candidates: keep it in registers and
+                // read the next path while the next candidate is being chosen
+                float cd[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int pos = 8 * k + static_cast<int>(gc.g);
+                    cd[k] = pos < count ? cand_d[deal_index(pos, beam)] : CUDART_INF_F;
+                }
+                unsigned ahead = 0xffffffffu;  // positions not yet passed
+                if (w == 0) {
+                    unsigned leaf = follow_bits<H, W>(o_lb);
+                    for (;;) {
+                        const ReplacePath<int2> path = replace_load<H, int2>(okey, oval, gc, leaf);
+                        const unsigned m = below_mask(cd, path.limit, gc) & ahead;
+                        const bool found = m != 0;
+                        if (!__any_sync(kFull, found)) break;
+                        const unsigned pos = found ? __ffs(m) - 1 : 0u;
+                        const float key = list_at(cd, pos);
+                        replace_apply<H, W>(okey, oval, o_sb, o_lb, gc, leaf, path, found, key,
+                                            slots[deal_index(pos, beam)]);
+                        if (found) ahead = 0xfffffffeu << pos;
+                        leaf = follow_bits<H, W>(o_lb);
+                    }
+                } else {
+                    for (;;) {
+                        const SinkPath<int32_t> path = sink_load<H, W, int32_t>(rkey, rid, r_sb, gc);
+                        const unsigned m = below_mask(cd, -r_root, gc) & ahead;
+                        const bool found = m != 0;
+                        if (!__any_sync(kFull, found)) break;
+                        const unsigned pos = found ? __ffs(m) - 1 : 0u;
+                        const float key = list_at(cd, pos);
+                        const float root = sink_apply<H, W, false>(
+                            rkey, rid, r_sb, r_sb, gc, path, found, -key,
+                            slots[deal_index(pos, beam)].x);
+                        if (found) { r_root = root; ahead = 0xfffffffeu << pos; }
+                    }
+                }
+            } else if (w == 0) {
                 unsigned leaf = follow_bits<H, W>(o_lb);
                 float limit = okey[leaf - 1];
                 for (;;) {
@@ -755,10 +880,10 @@ int traverse_packed_launch(int64_t *output_I, float *output_D, const int32_t *pa
                           d_model, n_neighbors, n_initials, ef_search);
     if (rc != PA_OK || batch == 0) return rc;
     PA_REQUIRE(packed_nbr && row_of, "null packed-index pointer");
-    PA_REQUIRE((reinterpret_cast<uintptr_t>(packed_nbr) & 7u) == 0,
-               "packed_nbr must be 8-byte aligned");
+    PA_REQUIRE((reinterpret_cast<uintptr_t>(packed_nbr) & 15u) == 0,
+               "packed_nbr must be 16-byte aligned");
     PA_REQUIRE(ldq >= d_model && ldq % 4 == 0, "query row stride must be a multiple of 4");
-    PackedLayout L{reinterpret_cast<const int2 *>(packed_nbr), row_of, storage, n_nodes};
+    PackedLayout L{reinterpret_cast<const int4 *>(packed_nbr), row_of, storage, n_nodes};
     return launch(L, output_I, output_D, query, ldq, initial_I, initial_D, batch, d_model,
                   n_neighbors, n_initials, ef_search, stats, stream);
 }

@@ -79,14 +79,16 @@ def traverse_cuda(output_I, output_D, indptr, indices, mapping, storage, query,
 
 def pack_graph(indptr, indices, mapping, n_storage: int, n_neighbors: int):
     """Packed device index from upstream's CSR tensors.  Returns
-    ``(packed_nbr int32 [n_storage, n_neighbors, 2], row_of int32 [n_nodes])``."""
+    ``(packed_nbr int32 [n_storage, n_neighbors, 4], row_of int32 [n_nodes])``:
+    per neighbour slot the global id, the storage row and two words of
+    precomputed bloom probes."""
     _check_cuda("indptr", indptr, 1, torch.int64)
     _check_cuda("indices", indices, 1, torch.int64)
     _check_cuda("mapping", mapping, 1, torch.int64)
     n_nodes = indptr.size(0) - 1
     _require(mapping.size(0) == n_nodes, "mapping.size(0) == n_nodes")
     dev = indptr.device
-    packed = torch.empty(n_storage, n_neighbors, 2, dtype=torch.int32, device=dev)
+    packed = torch.empty(n_storage, n_neighbors, 4, dtype=torch.int32, device=dev)
     row_of = torch.empty(n_nodes, dtype=torch.int32, device=dev)
     with torch.cuda.device(dev):
         _C.check(_C.lib().pa_pack_graph(
@@ -103,6 +105,7 @@ def traverse_packed(output_I, output_D, packed_nbr, row_of, storage, query, init
     _traverse_checks(output_I, output_D, storage, query, initial_I, initial_D, n_neighbors)
     _require(packed_nbr.size(0) == storage.size(0), "packed_nbr.size(0) == n_storage")
     _require(packed_nbr.size(1) == n_neighbors, "packed_nbr.size(1) == n_neighbors")
+    _require(packed_nbr.size(2) == 4, "packed_nbr.size(2) == 4")
     if stats is not None:
         _check_cuda("stats", stats, 2, torch.int32)
     with torch.cuda.device(query.device):
@@ -203,6 +206,7 @@ def search_reduced_noalloc(output_I, output_D, packed_nbr, row_of, storage, quer
     if route_vectors is not None:
         _check_cuda("route_vectors", route_vectors, 2, torch.float32)
     batch, d = query.shape
+    _require(packed_nbr.size(2) == 4, "packed_nbr.size(2) == 4")
     _require(storage.size(1) == d, "storage.size(-1) == d_principle")
     _require(output_I.shape == output_D.shape and output_I.size(0) == batch
              and output_I.size(1) == BEAM_WIDTH, "output shape [batch, 4, ef]")

@@ -96,8 +96,9 @@ class IndexStaged(nn.Module):
     # -- device residency (pilot_ann/layers/staged.py:124-139) -------------------
     def to(self, device, max_batch: int = 4096, max_ef: int = 256, n_streams: int = 2):
         """Uploads the reduced vectors of the sampled nodes, the entry tables,
-        the rotation, and the sub-graph in the packed layout (int32 id / row
-        pairs indexed by storage row); creates the per-device search stage."""
+        the rotation, and the sub-graph in the packed layout (per neighbour slot
+        int32 id, storage row and bloom probes, indexed by storage row); creates
+        the per-device search stage."""
         device = torch.device(device)
         self.cuda_device = device
         self.entry.to(device=device)

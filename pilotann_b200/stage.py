@@ -26,6 +26,8 @@ class SearchStage:
                 raise RuntimeError(f"{name} must be contiguous on {dev}")
         if packed_nbr.dtype != torch.int32 or row_of.dtype != torch.int32:
             raise RuntimeError("packed index must be int32")
+        if packed_nbr.dim() != 3 or packed_nbr.size(2) != 4:
+            raise RuntimeError("packed_nbr must be [n_storage, n_neighbors, 4] (extension.pack_graph)")
         if entry_nodes.dtype != torch.int64:
             raise RuntimeError("entry_nodes must be int64")
         for name in ("storage", "VT", "route_vectors", "entry_vectors"):
