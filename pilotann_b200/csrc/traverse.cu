@@ -21,14 +21,16 @@
 //   warp b  (every warp) loads the neighbour row of beam b together with its
 //           bloom probes (CSR layout: computes hashes and same-bit elections),
 //           so the four rows proceed in parallel;
-//   all warps: 16 teams of 8 lanes evaluate the distances of a round.
+//   all warps: 16 teams of 8 lanes evaluate the distances of the first 32
+//           survivors of a round; the open warp then starts inserting those
+//           while the other three warps evaluate the rest.
 // A heap operation is executed by a group of 8 lanes, one lane per level of the
 // root-to-leaf path, the four beams side by side in one warp.  The path is not
 // found by walking keys in shared memory: each heap keeps, in registers, one bit
 // per internal node for "right child smaller" and (open heaps) one for "right
 // child larger"; following them is a few integer instructions, after which every
 // lane derives its own node of the path by a shift (1-based heap indices).  The
-// bits of the nodes whose children changed are refreshed with one redux per
+// bits of the nodes whose children changed are refreshed with an 8-lane OR per
 // word.  The element layout of the heaps is exactly upstream's after every
 // operation (heapq.cuh:13-87), which is what makes evictions -- and therefore
 // results -- identical.
@@ -661,15 +663,17 @@ traverse_kernel(Layout L, int64_t *__restrict__ out_I, float *__restrict__ out_D
         const int n_work = n_work_s;
         if (n_work < kTeamsPerWarp) break;  // :182-184, uniform over the CTA
 
-        // distances (:187-204): 16 teams of 8 lanes, two candidates in flight each.
-        // The loop bound is the same for every lane of a warp (the team shuffles
-        // below name the whole warp); lanes past the end carry a false predicate.
-        {
+        // distances (:187-204) by teams of 8 lanes, two candidates in flight per
+        // team: team `team` of `n_teams` takes candidates j_begin + team,
+        // + n_teams, ... below j_end.  The loop bound is the same for every lane of
+        // a warp (the team shuffles name the whole warp); lanes past the end carry
+        // a false predicate.
+        auto distances = [&](int team, int n_teams, int j_begin, int j_end) {
             const int t8 = lane & 7;
-            for (int jb = w * kTeamsPerWarp; jb < n_work; jb += 2 * kBeams * kTeamsPerWarp) {
-                const int j0 = jb + (lane >> 3);
-                const int j1 = j0 + kBeams * kTeamsPerWarp;
-                const bool p0_in = j0 < n_work, p1_in = j1 < n_work;
+            for (int jb = j_begin; jb < j_end; jb += 2 * n_teams) {
+                const int j0 = jb + team;
+                const int j1 = j0 + n_teams;
+                const bool p0_in = j0 < j_end, p1_in = j1 < j_end;
                 int2 s0 = p0_in ? slots[j0] : make_int2(-1, -1);
                 int2 s1 = p1_in ? slots[j1] : make_int2(-1, -1);
                 if constexpr (!Layout::kPacked) {
@@ -712,45 +716,77 @@ traverse_kernel(Layout L, int64_t *__restrict__ out_I, float *__restrict__ out_D
                     if (p1_in) cand_d[j1] = p1 ? a1 : CUDART_INF_F;
                 }
             }
-        }
-        __syncthreads();
+        };
+        const int count = deal_count(n_work, beam);  // length of this group's beam list
 
-        // heap inserts (:206-220): candidate j -> beam (j / 4) mod 4, ascending j.
-        // Each group walks its beam's list, skipping the candidates its heap would
-        // turn down, so that a step of the warp is an operation that changes a heap.
-        if (w < 2) {
-            const int count = deal_count(n_work, beam);
-            int s = 0;
-            if (w == 0) {
-                int valid = 0;
-                for (int j = lane; j < n_work; j += 32) valid += slots[j].y >= 0;
-                n_eval += __reduce_add_sync(kFull, valid);
+        if constexpr (CH == 1) {
+            // Heap inserts (:206-220): candidate j -> beam (j / 4) mod 4, ascending j;
+            // each group walks its beam's list, skipping the candidates its heap
+            // would turn down, so that a step of the warp is an operation that changes
+            // a heap.  A beam's list has at most 32 candidates: it is kept in
+            // registers (lane g: positions g, g + 8, g + 16, g + 24), and the next
+            // path is read while the next candidate is being chosen.
+            // The first 32 candidates are exactly positions 0-7 of the four lists.
+            // All warps evaluate those; then the open warp starts on them while the
+            // other three warps evaluate the rest (named barrier 2: 96 threads arrive,
+            // the open warp waits when it has used up positions 0-7), and the result
+            // warp inserts once everything is known (named barrier 3 among those
+            // three warps).  Both barriers complete once per round, and a warp cannot
+            // reach the next round's use before the CTA-wide barriers in between.
+            constexpr int kFirst = 2 * kBeams * kTeamsPerWarp;  // 32
+            distances(w * kTeamsPerWarp + (lane >> 3), kBeams * kTeamsPerWarp, 0,
+                      min(n_work, kFirst));
+            __syncthreads();
+            const bool more = n_work > kFirst;  // uniform over the CTA
+            if (w != 0 && more) {
+                distances((w - 1) * kTeamsPerWarp + (lane >> 3), (kBeams - 1) * kTeamsPerWarp,
+                          kFirst, n_work);
+                __threadfence_block();
+                asm volatile("bar.arrive 2, 128;" ::: "memory");  // to the open warp
+                if (w == 1) asm volatile("bar.sync 3, 96;" ::: "memory");  // result warp waits
+                else asm volatile("bar.arrive 3, 96;" ::: "memory");       // for the other two
             }
-            if constexpr (CH == 1) {
-                // a beam's list has at most 32 candidates: keep it in registers and
-                // read the next path while the next candidate is being chosen
+            if (w < 2) {
                 float cd[4];
+                auto load_list = [&](int k_from) {
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const int pos = 8 * k + static_cast<int>(gc.g);
-                    cd[k] = pos < count ? cand_d[deal_index(pos, beam)] : CUDART_INF_F;
-                }
+                    for (int k = 0; k < 4; ++k) {
+                        const int pos = 8 * k + static_cast<int>(gc.g);
+                        if (k >= k_from)
+                            cd[k] = pos < count ? cand_d[deal_index(pos, beam)] : CUDART_INF_F;
+                    }
+                };
                 unsigned ahead = 0xffffffffu;  // positions not yet passed
                 if (w == 0) {
                     unsigned leaf = follow_bits<H, W>(o_lb);
-                    for (;;) {
-                        const ReplacePath<int2> path = replace_load<H, int2>(okey, oval, gc, leaf);
-                        const unsigned m = below_mask(cd, path.limit, gc) & ahead;
-                        const bool found = m != 0;
-                        if (!__any_sync(kFull, found)) break;
-                        const unsigned pos = found ? __ffs(m) - 1 : 0u;
-                        const float key = list_at(cd, pos);
-                        replace_apply<H, W>(okey, oval, o_sb, o_lb, gc, leaf, path, found, key,
-                                            slots[deal_index(pos, beam)]);
-                        if (found) ahead = 0xfffffffeu << pos;
-                        leaf = follow_bits<H, W>(o_lb);
+                    auto run = [&]() {
+                        for (;;) {
+                            const ReplacePath<int2> path =
+                                replace_load<H, int2>(okey, oval, gc, leaf);
+                            const unsigned m = below_mask(cd, path.limit, gc) & ahead;
+                            const bool found = m != 0;
+                            if (!__any_sync(kFull, found)) break;
+                            const unsigned pos = found ? __ffs(m) - 1 : 0u;
+                            const float key = list_at(cd, pos);
+                            replace_apply<H, W>(okey, oval, o_sb, o_lb, gc, leaf, path, found, key,
+                                                slots[deal_index(pos, beam)]);
+                            if (found) ahead = 0xfffffffeu << pos;
+                            leaf = follow_bits<H, W>(o_lb);
+                        }
+                    };
+                    load_list(0);
+                    if (more) {
+                        cd[1] = cd[2] = cd[3] = CUDART_INF_F;  // not evaluated yet
+                        run();
+                        asm volatile("bar.sync 2, 128;" ::: "memory");
+                        load_list(1);
                     }
+                    run();
+                    int valid = 0;
+                    for (int j = lane; j < n_work; j += 32) valid += slots[j].y >= 0;
+                    n_eval += __reduce_add_sync(kFull, valid);
                 } else {
+                    load_list(0);
                     for (;;) {
                         const SinkPath<int32_t> path = sink_load<H, W, int32_t>(rkey, rid, r_sb, gc);
                         const unsigned m = below_mask(cd, -r_root, gc) & ahead;
@@ -764,32 +800,43 @@ traverse_kernel(Layout L, int64_t *__restrict__ out_I, float *__restrict__ out_D
                         if (found) { r_root = root; ahead = 0xfffffffeu << pos; }
                     }
                 }
-            } else if (w == 0) {
-                unsigned leaf = follow_bits<H, W>(o_lb);
-                float limit = okey[leaf - 1];
-                for (;;) {
-                    s = next_below(cand_d, gc, beam, s, count, limit);
-                    const bool found = s < count;
-                    if (!__any_sync(kFull, found)) break;
-                    const int j = found ? deal_index(s, beam) : 0;
-                    group_replace_at<H, W>(okey, oval, o_sb, o_lb, gc, leaf, found, cand_d[j],
-                                           slots[j]);
-                    s += found;
-                    leaf = follow_bits<H, W>(o_lb);
-                    limit = okey[leaf - 1];
-                }
-            } else {
-                for (;;) {
-                    s = next_below(cand_d, gc, beam, s, count, -r_root);
-                    const bool found = s < count;
-                    if (!__any_sync(kFull, found)) break;
-                    const int j = found ? deal_index(s, beam) : 0;
-                    const float root = group_sink<H, W, false>(rkey, rid, r_sb, r_sb, gc, found,
-                                                               -cand_d[j], slots[j].x);
-                    if (found) { r_root = root; ++s; }
-                }
+                pair_sync();  // result roots visible to the open warp before it pops
             }
-            pair_sync();  // result roots visible to the open warp before it pops
+        } else {
+            distances(w * kTeamsPerWarp + (lane >> 3), kBeams * kTeamsPerWarp, 0, n_work);
+            __syncthreads();
+            if (w < 2) {
+                int s = 0;
+                if (w == 0) {
+                    int valid = 0;
+                    for (int j = lane; j < n_work; j += 32) valid += slots[j].y >= 0;
+                    n_eval += __reduce_add_sync(kFull, valid);
+                    unsigned leaf = follow_bits<H, W>(o_lb);
+                    float limit = okey[leaf - 1];
+                    for (;;) {
+                        s = next_below(cand_d, gc, beam, s, count, limit);
+                        const bool found = s < count;
+                        if (!__any_sync(kFull, found)) break;
+                        const int j = found ? deal_index(s, beam) : 0;
+                        group_replace_at<H, W>(okey, oval, o_sb, o_lb, gc, leaf, found, cand_d[j],
+                                               slots[j]);
+                        s += found;
+                        leaf = follow_bits<H, W>(o_lb);
+                        limit = okey[leaf - 1];
+                    }
+                } else {
+                    for (;;) {
+                        s = next_below(cand_d, gc, beam, s, count, -r_root);
+                        const bool found = s < count;
+                        if (!__any_sync(kFull, found)) break;
+                        const int j = found ? deal_index(s, beam) : 0;
+                        const float root = group_sink<H, W, false>(rkey, rid, r_sb, r_sb, gc, found,
+                                                                   -cand_d[j], slots[j].x);
+                        if (found) { r_root = root; ++s; }
+                    }
+                }
+                pair_sync();  // result roots visible to the open warp before it pops
+            }
         }
     }
     __syncthreads();
