@@ -44,7 +44,7 @@ OPERATING_EF = {1: 32, 2: 128, 3: 128}
 # ncu dram__bytes_read.sum + dram__bytes_write.sum per traversal launch divided by
 # the queries in that launch (bytes / query), from the capture summarised under
 # profiles/; None until captured
-NCU_TRAFFIC_PER_QUERY = {2: 1.312231e9 / 1024}   # profiles/traverse_kernel_c2-1m-768-cos_ef128.md
+NCU_TRAFFIC_PER_QUERY = {2: 1.497034e9 / 1024}   # profiles/traverse_kernel_c2-1m-768-cos_ef128.md
 FALLBACK_HBM_GBS = 6650.0
 
 
