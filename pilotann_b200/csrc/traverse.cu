@@ -67,6 +67,7 @@ struct PackedLayout {
 
 constexpr int kThreads = kBeams * 32;
 constexpr int kGroup = 8;  // lanes per heap operation
+template <int H> constexpr int kHeapRow = H + kGroup;  // heap + the group's spare slots
 constexpr unsigned kFull = 0xffffffffu;
 
 template <int H> struct HeapShape {
@@ -146,7 +147,8 @@ struct GroupCtx {
 };
 
 // ---- heap operations, one group of 8 lanes per heap --------------------------
-// K / V: the heap's arrays in shared memory (0-based storage of 1-based nodes).
+// K / V: the heap's arrays in shared memory (0-based storage of 1-based nodes),
+// followed by one spare slot per lane of the group (kHeapRow entries in all).
 // sb / lb: "right child smaller" / "right child larger" bits.
 
 // Puts (k, v) at the root and sinks it (upstream __heapify_up, heapq.cuh:13-29).
@@ -194,12 +196,15 @@ __device__ __forceinline__ float sink_apply(float *K, V *Vv, uint32_t (&sb)[W], 
     const float a_next = __shfl_down_sync(kFull, a, 1, kGroup);
     const float a_first = __shfl_sync(kFull, a, 0, kGroup);
     const bool moves = on && t <= cnt;
-    if (moves) { K[(node >> 1) - 1] = a; Vv[(node >> 1) - 1] = p.av; }
-    if (active && t == max(cnt, 1u)) {
-        // cnt == 0: the new element stays at the root (written by level-1 lane)
-        const unsigned at = cnt == 0 ? 1u : node;
-        K[at - 1] = k; Vv[at - 1] = v;
-    }
+    // Stores are unconditional: a lane with nothing to write aims at its own
+    // spare slot behind the heap.  A store under a lane-dependent condition
+    // makes the warp diverge, which costs far more than the store.
+    const unsigned spare = static_cast<unsigned>(H) + c.g;
+    const unsigned up = moves ? (node >> 1) - 1 : spare;
+    K[up] = a; Vv[up] = p.av;
+    // cnt == 0: the new element stays at the root (written by level-1 lane)
+    const unsigned at = (active && t == max(cnt, 1u)) ? (cnt == 0 ? 1u : node) - 1 : spare;
+    K[at] = k; Vv[at] = v;
     // refresh the bits of the parents of the moved nodes (path levels 0 .. cnt-1)
     const float nk = (t == cnt) ? k : a_next;  // new key at this lane's node
     const bool odd = node & 1u;
@@ -266,12 +271,13 @@ __device__ __forceinline__ void replace_apply(float *K, V *Vv, uint32_t (&sb)[W]
     const unsigned cm = (__ballot_sync(kFull, on && b > k) >> c.gshift) & 0xffu;
     const unsigned s = cm ? (__ffs(cm) - 1) : L;  // level where the new element lands
     const bool moves = on && t >= s;
-    if (moves) { K[child - 1] = b; Vv[child - 1] = p.bv; }
-    if (accept && t == min(s, L - 1u)) {
-        // s == L: nothing moves, the new element replaces the leaf (level L-1 lane)
-        const unsigned at = s == L ? leaf : node;
-        K[at - 1] = k; Vv[at - 1] = v;
-    }
+    // unconditional stores, spare slot for lanes with nothing to write (see sink_apply)
+    const unsigned spare = static_cast<unsigned>(H) + c.g;
+    const unsigned down = moves ? child - 1 : spare;
+    K[down] = b; Vv[down] = p.bv;
+    // s == L: nothing moves, the new element replaces the leaf (level L-1 lane)
+    const unsigned at = (accept && t == min(s, L - 1u)) ? (s == L ? leaf : node) - 1 : spare;
+    K[at] = k; Vv[at] = v;
     // parents whose path child changed: levels max(s-1, 0) .. L-1
     const float nk = (t + 1u == s) ? k : b;  // new key of this lane's path child
     const bool odd = child & 1u;
@@ -426,12 +432,15 @@ traverse_kernel(Layout L, int64_t *__restrict__ out_I, float *__restrict__ out_D
     constexpr int W = HeapShape<H>::kWords;
     constexpr int n_nb = 32 * CH;
     __shared__ uint32_t bloom[kBloomWords];
-    __shared__ float open_key[kBeams][H];
-    __shared__ int2 open_val[kBeams][H];  // {global id, storage row}
-    __shared__ float res_key[kBeams][H];
-    __shared__ int32_t res_id[kBeams][H];
-    __shared__ int2 slots[kBeams * n_nb];  // survivors {global id, storage row}
-    __shared__ float cand_d[kBeams * n_nb];
+    __shared__ float open_key[kBeams][kHeapRow<H>];
+    __shared__ int2 open_val[kBeams][kHeapRow<H>];  // {global id, storage row}
+    __shared__ float res_key[kBeams][kHeapRow<H>];
+    __shared__ int32_t res_id[kBeams][kHeapRow<H>];
+    // survivors {global id, storage row} and their distances; the last 32 entries
+    // are spare slots, one per lane, for stores that have nothing to write
+    constexpr int kSpare = kBeams * n_nb;
+    __shared__ int2 slots[kBeams * n_nb + 32];
+    __shared__ float cand_d[kBeams * n_nb + 32];
     __shared__ int n_work_s;
     __shared__ uint2 probe_s[kBeams * n_nb];  // packed bloom probes of a round's slots
     __shared__ PopSlot pop_s[kBeams];
@@ -450,10 +459,10 @@ traverse_kernel(Layout L, int64_t *__restrict__ out_I, float *__restrict__ out_D
     for (int i = threadIdx.x; i < kBloomWords; i += kThreads) bloom[i] = 0;
     for (int i = threadIdx.x; i < d; i += kThreads) q_s[i] = query[b * ldq + i];
     for (int i = threadIdx.x; i < kBeams * H; i += kThreads) {
-        (&open_key[0][0])[i] = CUDART_INF_F;
-        (&open_val[0][0])[i] = make_int2(-1, -1);
-        (&res_key[0][0])[i] = -CUDART_INF_F;
-        (&res_id[0][0])[i] = -1;
+        open_key[i / H][i % H] = CUDART_INF_F;
+        open_val[i / H][i % H] = make_int2(-1, -1);
+        res_key[i / H][i % H] = -CUDART_INF_F;
+        res_id[i / H][i % H] = -1;
     }
     if (threadIdx.x < 4) stat_s[threadIdx.x] = 0;
     if (threadIdx.x < 2) again_s[threadIdx.x] = 0;
@@ -558,12 +567,12 @@ traverse_kernel(Layout L, int64_t *__restrict__ out_I, float *__restrict__ out_D
                     }
                 }
                 pending = false;
-                if (gc.g == 0) {
-                    pop_s[beam].node = u_node; pop_s[beam].row = u_row;
-                    pop_s[beam].lo = u_lo; pop_s[beam].len = u_len;
-                    pop_s[beam].fetch = fetch;
-                }
-                if (lane == 0) again_s[(outer + 1) & 1] = 0;
+                // group-uniform values: every lane of the group stores them (same
+                // address, same value) rather than one lane under a condition
+                pop_s[beam].node = u_node; pop_s[beam].row = u_row;
+                pop_s[beam].lo = u_lo; pop_s[beam].len = u_len;
+                pop_s[beam].fetch = fetch;
+                again_s[(outer + 1) & 1] = 0;
             }
             __syncthreads();
             if (pop_s[w].fetch) {  // warp w serves beam w
@@ -631,17 +640,16 @@ traverse_kernel(Layout L, int64_t *__restrict__ out_I, float *__restrict__ out_D
                     miss[bb] = 0;
 #pragma unroll
                     for (int s = 0; s < kFnvSteps; ++s) {
-                        if ((pr.elected >> s) & 1u) {
-                            const uint32_t bit = 1u << (pr.pos[s] & 31);
-                            miss[bb] |= ~atomicOr(&bloom[pr.pos[s] >> 5], bit) & bit;
-                        }
+                        // a lane that is not elected ORs in nothing: no branch
+                        const uint32_t bit = ((pr.elected >> s) & 1u) << (pr.pos[s] & 31);
+                        miss[bb] |= ~atomicOr(&bloom[pr.pos[s] >> 5], bit) & bit;
                         __syncwarp();
                     }
                 }
 #pragma unroll
                 for (int bb = 0; bb < kBeams; ++bb) {
                     const unsigned m = __ballot_sync(kFull, miss[bb] != 0);
-                    if (miss[bb] != 0) slots[off + __popc(m & ((1u << lane) - 1u))] = ev[bb];
+                    slots[miss[bb] != 0 ? off + __popc(m & ((1u << lane) - 1u)) : kSpare + lane] = ev[bb];
                     off += __popc(m);
                 }
             } else
@@ -657,7 +665,7 @@ traverse_kernel(Layout L, int64_t *__restrict__ out_I, float *__restrict__ out_D
                     off += __popc(m);
                 }
             }
-            if (lane == 0) n_work_s = off;
+            n_work_s = off;  // warp-uniform
         }
         __syncthreads();
         const int n_work = n_work_s;
@@ -711,10 +719,8 @@ traverse_kernel(Layout L, int64_t *__restrict__ out_I, float *__restrict__ out_D
                 a0 = team_reduce(a0);
                 a1 = team_reduce(a1);
                 // +inf marks a candidate without a vector: it is never inserted
-                if (t8 == 0) {
-                    if (p0_in) cand_d[j0] = p0 ? a0 : CUDART_INF_F;
-                    if (p1_in) cand_d[j1] = p1 ? a1 : CUDART_INF_F;
-                }
+                cand_d[(t8 == 0 && p0_in) ? j0 : kSpare + lane] = p0 ? a0 : CUDART_INF_F;
+                cand_d[(t8 == 0 && p1_in) ? j1 : kSpare + lane] = p1 ? a1 : CUDART_INF_F;
             }
         };
         const int count = deal_count(n_work, beam);  // length of this group's beam list
@@ -842,19 +848,36 @@ traverse_kernel(Layout L, int64_t *__restrict__ out_I, float *__restrict__ out_D
     __syncthreads();
 
     // ---- store (:230-245): per beam worst -> best ----------------------------------
+    // The result warp pops into the rows of the open heaps' values, which are dead
+    // by now; all threads then write the output with coalesced stores.
+    const int n_discard = max(H - ef, 0), n_real = min(ef, H);
     if (w == 1) {
-        int64_t *oI = out_I + (b * kBeams + beam) * ef;
-        float *oD = out_D + (b * kBeams + beam) * ef;
-        const int n_discard = max(H - ef, 0), n_real = min(ef, H);
         for (int p = 0; p < n_discard + n_real; ++p) {
             const float key = rkey[0];
             const int32_t id = rid[0];
             group_sink<H, W, false>(rkey, rid, r_sb, r_sb, gc, true, CUDART_INF_F, int32_t(-1));
             const int i = p - n_discard;
-            if (i >= 0 && gc.g == 0) { oI[i] = id; oD[i] = -key; }
+            oval[(i >= 0 && gc.g == 0) ? i : H + static_cast<int>(gc.g)] =
+                make_int2(id, __float_as_int(-key));
+        }
+    }
+    __syncthreads();
+    {
+        int64_t *oI = out_I + b * kBeams * ef;
+        float *oD = out_D + b * kBeams * ef;
+        for (int i = threadIdx.x; i < kBeams * n_real; i += kThreads) {
+            const int bm = i / n_real, j = i - bm * n_real;
+            const int2 e = open_val[bm][j];
+            oI[bm * ef + j] = e.x;
+            oD[bm * ef + j] = __int_as_float(e.y);
         }
         // ef > H: the heap is exhausted, upstream keeps popping (-1, key +inf)
-        for (int i = H + gc.g; i < ef; i += kGroup) { oI[i] = -1; oD[i] = -CUDART_INF_F; }
+        const int n_tail = ef - n_real;
+        for (int i = threadIdx.x; i < kBeams * n_tail; i += kThreads) {
+            const int bm = i / n_tail, j = n_real + (i - bm * n_tail);
+            oI[bm * ef + j] = -1;
+            oD[bm * ef + j] = -CUDART_INF_F;
+        }
     }
     if (stats != nullptr) {
         __syncthreads();
