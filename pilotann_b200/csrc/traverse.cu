@@ -550,21 +550,27 @@ traverse_kernel(Layout L, int64_t *__restrict__ out_I, float *__restrict__ out_D
                     const int2 top_v = oval[0];
                     group_sink<H, W, true>(okey, oval, o_sb, o_lb, gc, pending, CUDART_INF_F,
                                            make_int2(-1, -1));
-                    if (pending) {
-                        if (top_v.x < 0 || top_k >= bound) {
-                            pending = false; u_node = -1; u_row = -1; u_len = 0;
-                        } else if constexpr (Layout::kPacked) {
-                            if (top_v.y >= 0) { pending = false; u_node = top_v.x; u_row = top_v.y; }
-                        } else {
-                            const int64_t lo = __ldg(L.indptr + top_v.x);
-                            const int64_t hi = __ldg(L.indptr + top_v.x + 1);
-                            if (lo != hi) {
-                                pending = false; u_node = top_v.x; u_lo = lo;
-                                u_len = static_cast<int>(min(hi - lo, static_cast<int64_t>(n_nb)));
-                            }
-                        }
-                        if (!pending) fetch = true;
+                    // written as selects: the groups of the warp disagree on all of
+                    // these conditions, and a branch on them would split the warp
+                    const bool stop = top_v.x < 0 || top_k >= bound;  // the beam gives up
+                    bool usable;  // the popped node has an adjacency row
+                    int64_t lo = 0, hi = 0;
+                    if constexpr (Layout::kPacked) {
+                        usable = top_v.y >= 0;
+                    } else {
+                        const int64_t at = (pending && !stop) ? top_v.x : 0;
+                        lo = __ldg(L.indptr + at);
+                        hi = __ldg(L.indptr + min(at + 1, L.n_nodes));  // indptr has n_nodes + 1 entries
+                        usable = lo != hi;
                     }
+                    const bool settle = pending && (stop || usable);
+                    u_node = settle ? (stop ? -1 : top_v.x) : u_node;
+                    u_row = settle ? (stop ? -1 : top_v.y) : u_row;
+                    u_lo = (settle && !stop) ? lo : u_lo;
+                    u_len = settle ? (stop ? 0 : static_cast<int>(min(hi - lo, static_cast<int64_t>(n_nb))))
+                                   : u_len;
+                    fetch = fetch || settle;
+                    pending = pending && !settle;
                 }
                 pending = false;
                 // group-uniform values: every lane of the group stores them (same
@@ -682,15 +688,15 @@ traverse_kernel(Layout L, int64_t *__restrict__ out_I, float *__restrict__ out_D
                 const int j0 = jb + team;
                 const int j1 = j0 + n_teams;
                 const bool p0_in = j0 < j_end, p1_in = j1 < j_end;
-                int2 s0 = p0_in ? slots[j0] : make_int2(-1, -1);
-                int2 s1 = p1_in ? slots[j1] : make_int2(-1, -1);
+                // Lanes past the end or without a vector read row 0 and drop the
+                // result: every load below is unconditional, no lane-dependent branch.
+                // (j0, j1 stay inside the arrays: they are below j_end + 2 * n_teams.)
+                int2 s0 = slots[j0], s1 = slots[j1];
                 if constexpr (!Layout::kPacked) {
-                    if (p0_in) s0.y = static_cast<int32_t>(__ldg(L.mapping + s0.x));
-                    if (p1_in) s1.y = static_cast<int32_t>(__ldg(L.mapping + s1.x));
-                    if (t8 == 0) {
-                        if (p0_in) slots[j0].y = s0.y;
-                        if (p1_in) slots[j1].y = s1.y;
-                    }
+                    s0.y = static_cast<int32_t>(__ldg(L.mapping + (p0_in ? s0.x : 0)));
+                    s1.y = static_cast<int32_t>(__ldg(L.mapping + (p1_in ? s1.x : 0)));
+                    slots[(t8 == 0 && p0_in) ? j0 : kSpare + lane].y = s0.y;
+                    slots[(t8 == 0 && p1_in) ? j1 : kSpare + lane].y = s1.y;
                 }
                 const bool p0 = p0_in && s0.y >= 0, p1 = p1_in && s1.y >= 0;
                 const float *r0 = L.storage + static_cast<int64_t>(p0 ? s0.y : 0) * d;
@@ -702,10 +708,10 @@ traverse_kernel(Layout L, int64_t *__restrict__ out_I, float *__restrict__ out_D
 #pragma unroll
                     for (int m = 0; m < 4; ++m) {
                         const bool in = o + 32 * m < d;
-                        x0[m] = (p0 && in) ? __ldg(reinterpret_cast<const float4 *>(r0 + o + 32 * m))
-                                           : make_float4(0, 0, 0, 0);
-                        x1[m] = (p1 && in) ? __ldg(reinterpret_cast<const float4 *>(r1 + o + 32 * m))
-                                           : make_float4(0, 0, 0, 0);
+                        x0[m] = in ? __ldg(reinterpret_cast<const float4 *>(r0 + o + 32 * m))
+                                   : make_float4(0, 0, 0, 0);
+                        x1[m] = in ? __ldg(reinterpret_cast<const float4 *>(r1 + o + 32 * m))
+                                   : make_float4(0, 0, 0, 0);
                     }
 #pragma unroll
                     for (int m = 0; m < 4; ++m) {
@@ -758,8 +764,10 @@ traverse_kernel(Layout L, int64_t *__restrict__ out_I, float *__restrict__ out_D
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
                         const int pos = 8 * k + static_cast<int>(gc.g);
-                        if (k >= k_from)
-                            cd[k] = pos < count ? cand_d[deal_index(pos, beam)] : CUDART_INF_F;
+                        if (k >= k_from) {  // compile-time after unrolling
+                            const float dist = cand_d[deal_index(pos, beam)];  // in bounds
+                            cd[k] = pos < count ? dist : CUDART_INF_F;
+                        }
                     }
                 };
                 unsigned ahead = 0xffffffffu;  // positions not yet passed
@@ -789,7 +797,8 @@ traverse_kernel(Layout L, int64_t *__restrict__ out_I, float *__restrict__ out_D
                     }
                     run();
                     int valid = 0;
-                    for (int j = lane; j < n_work; j += 32) valid += slots[j].y >= 0;
+                    for (int jb = 0; jb < n_work; jb += 32)  // slots[jb + lane] is in bounds
+                        valid += (jb + lane < n_work) & (slots[jb + lane].y >= 0);
                     n_eval += __reduce_add_sync(kFull, valid);
                 } else {
                     load_list(0);
