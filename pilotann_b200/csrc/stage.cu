@@ -17,6 +17,8 @@ struct pa_stage {
     int64_t max_batch = 0;
     int max_ef = 0;
     std::vector<cudaStream_t> streams;
+    cudaStream_t copy_stream = nullptr;     // carries the rotated queries back while a chunk searches
+    std::vector<cudaEvent_t> projected;     // per stream: the chunk's rotated queries are ready
     float *d_raw = nullptr;      // [max_batch, d_model] raw queries (copy-in target)
     float *d_rot = nullptr;      // [max_batch, d_model] rotated queries
     int64_t *d_router = nullptr; // [max_batch]
@@ -51,7 +53,8 @@ struct DeviceScope {
 // [0, n) of the given buffers, all on one stream.
 static int enqueue_chunk(pa_stage *st, const float *raw, float *rot, int64_t *router,
                          float *dots, float *ep_D, int64_t *ep_I, int64_t *out_I, float *out_D, int64_t n,
-                         int ef, int32_t *stats, cudaStream_t stream) {
+                         int ef, int32_t *stats, cudaStream_t stream,
+                         cudaEvent_t projected = nullptr) {
     const pa_stage_index &ix = st->ix;
     const float *rotated = raw;
     if (ix.VT != nullptr) {
@@ -59,6 +62,7 @@ static int enqueue_chunk(pa_stage *st, const float *raw, float *rot, int64_t *ro
         if (rc != PA_OK) return rc;
         rotated = rot;
     }
+    if (projected != nullptr) PA_CUDA_TRY(cudaEventRecord(projected, stream));
     int rc = route_launch(router, ep_D, ep_I, rotated, ix.d_model, ix.route_vectors,
                           ix.entry_nodes, ix.entry_vectors, n, ix.d_principle,
                           ix.route_vectors ? ix.n_routers : 1, ix.n_leaves, dots, st->d_rnorm,
@@ -112,7 +116,13 @@ extern "C" int pa_stage_create(pa_stage **out, const pa_stage_index *index, int6
         e = cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking);
         if (e != cudaSuccess) return bail(e, "cudaStreamCreateWithFlags");
         st->streams.push_back(s);
+        cudaEvent_t ev;
+        e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+        if (e != cudaSuccess) return bail(e, "cudaEventCreateWithFlags");
+        st->projected.push_back(ev);
     }
+    e = cudaStreamCreateWithFlags(&st->copy_stream, cudaStreamNonBlocking);
+    if (e != cudaSuccess) return bail(e, "cudaStreamCreateWithFlags");
     const size_t B = static_cast<size_t>(max_batch);
     const size_t row = sizeof(float) * ix.d_model;
     const size_t out_elems = B * PA_BEAMS * max_ef;
@@ -150,6 +160,11 @@ extern "C" void pa_stage_destroy(pa_stage *st) {
         cudaStreamSynchronize(s);
         cudaStreamDestroy(s);
     }
+    if (st->copy_stream != nullptr) {
+        cudaStreamSynchronize(st->copy_stream);
+        cudaStreamDestroy(st->copy_stream);
+    }
+    for (cudaEvent_t ev : st->projected) cudaEventDestroy(ev);
     cudaFree(st->d_raw);
     cudaFree(st->d_rot);
     cudaFree(st->d_router);
@@ -188,17 +203,25 @@ extern "C" int pa_stage_search(pa_stage *st, const float *host_query, float *hos
                            st->d_dots ? st->d_dots + lo * ix.n_routers : nullptr,
                            st->d_ep_D + lo * ix.n_leaves,
                            st->d_ep_I + lo * ix.n_leaves, st->d_out_I + lo * out_row,
-                           st->d_out_D + lo * out_row, m, ef, nullptr, s);
+                           st->d_out_D + lo * out_row, m, ef, nullptr, s,
+                           st->projected[n % st->streams.size()]);
         if (rc != PA_OK) return rc;
-        if (host_rotated != nullptr)
+        if (host_rotated != nullptr) {
+            // the rotated queries travel back on their own stream while the chunk
+            // is still routing and traversing
+            PA_CUDA_TRY(cudaStreamWaitEvent(st->copy_stream,
+                                            st->projected[n % st->streams.size()], 0));
             PA_CUDA_TRY(cudaMemcpyAsync(host_rotated + lo * d, rot ? rot : raw,
-                                        sizeof(float) * m * d, cudaMemcpyDeviceToHost, s));
+                                        sizeof(float) * m * d, cudaMemcpyDeviceToHost,
+                                        st->copy_stream));
+        }
         PA_CUDA_TRY(cudaMemcpyAsync(host_out_I + lo * out_row, st->d_out_I + lo * out_row,
                                     sizeof(int64_t) * m * out_row, cudaMemcpyDeviceToHost, s));
         PA_CUDA_TRY(cudaMemcpyAsync(host_out_D + lo * out_row, st->d_out_D + lo * out_row,
                                     sizeof(float) * m * out_row, cudaMemcpyDeviceToHost, s));
     }
     for (cudaStream_t s : st->streams) PA_CUDA_TRY(cudaStreamSynchronize(s));
+    PA_CUDA_TRY(cudaStreamSynchronize(st->copy_stream));
     return PA_OK;
 }
 
@@ -221,6 +244,7 @@ extern "C" int pa_stage_synchronize(pa_stage *st) {
     pa::DeviceScope scope;
     PA_CUDA_TRY(scope.enter(st->device));
     for (cudaStream_t s : st->streams) PA_CUDA_TRY(cudaStreamSynchronize(s));
+    PA_CUDA_TRY(cudaStreamSynchronize(st->copy_stream));
     return PA_OK;
 }
 

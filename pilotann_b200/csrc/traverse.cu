@@ -424,7 +424,10 @@ __device__ __forceinline__ float list_at(const float (&cd)[4], unsigned p) {
 }
 
 template <int H, int CH, class Layout>
-__global__ void __launch_bounds__(kThreads, 7)
+#ifndef PA_MIN_CTAS
+#define PA_MIN_CTAS 7
+#endif
+__global__ void __launch_bounds__(kThreads, PA_MIN_CTAS)
 traverse_kernel(Layout L, int64_t *__restrict__ out_I, float *__restrict__ out_D,
                 const float *__restrict__ query, const int64_t *__restrict__ init_I,
                 const float *__restrict__ init_D, int d, int64_t ldq, int n_init, int ef,
