@@ -66,6 +66,11 @@ struct PackedLayout {
 };
 
 constexpr int kThreads = kBeams * 32;
+// CTAs per SM the kernel is compiled for (register cap 65536 / (128 * n)): 7 is
+// right when a batch is one wave (1024 queries on 148 SMs = 6.9 CTAs per SM).
+#ifndef PA_MIN_CTAS
+#define PA_MIN_CTAS 7
+#endif
 constexpr int kGroup = 8;  // lanes per heap operation
 template <int H> constexpr int kHeapRow = H + kGroup;  // heap + the group's spare slots
 constexpr unsigned kFull = 0xffffffffu;
@@ -339,11 +344,10 @@ __device__ __forceinline__ bool bloom_commit(uint32_t *bloom, const BloomProbe &
     bool found = true;
 #pragma unroll
     for (int s = 0; s < kFnvSteps; ++s) {
-        if ((p.elected >> s) & 1u) {
-            const uint32_t bit = 1u << (p.pos[s] & 31);
-            const uint32_t old = atomicOr(&bloom[p.pos[s] >> 5], bit);
-            found = found && (old & bit);
-        }
+        // a lane that is not elected ORs in nothing and passes: no branch
+        const uint32_t bit = ((p.elected >> s) & 1u) << (p.pos[s] & 31);
+        const uint32_t old = atomicOr(&bloom[p.pos[s] >> 5], bit);
+        found = found && (old & bit) == bit;
         __syncwarp();
     }
     return found;
@@ -373,7 +377,6 @@ __device__ __forceinline__ void pair_sync() {  // warps 0 and 1 only
 
 // Candidates are dealt to the beams four at a time (candidate j -> beam
 // (j / 4) mod 4); beam 0 always holds the most.
-__device__ __forceinline__ int deal_steps(int n) { return 4 * (n >> 4) + min(4, n & 15); }
 __device__ __forceinline__ int deal_index(int s, int beam) {
     return 16 * (s >> 2) + 4 * beam + (s & 3);
 }
@@ -424,9 +427,6 @@ __device__ __forceinline__ float list_at(const float (&cd)[4], unsigned p) {
 }
 
 template <int H, int CH, class Layout>
-#ifndef PA_MIN_CTAS
-#define PA_MIN_CTAS 7
-#endif
 __global__ void __launch_bounds__(kThreads, PA_MIN_CTAS)
 traverse_kernel(Layout L, int64_t *__restrict__ out_I, float *__restrict__ out_D,
                 const float *__restrict__ query, const int64_t *__restrict__ init_I,
@@ -670,7 +670,7 @@ traverse_kernel(Layout L, int64_t *__restrict__ out_I, float *__restrict__ out_D
                     const int2 e = slots[idx];
                     const bool seen = bloom_commit(bloom, probe_unpack(probe_s[idx]));
                     const unsigned m = __ballot_sync(kFull, !seen);
-                    if (!seen) slots[off + __popc(m & ((1u << lane) - 1u))] = e;
+                    slots[!seen ? off + __popc(m & ((1u << lane) - 1u)) : kSpare + lane] = e;
                     off += __popc(m);
                 }
             }
