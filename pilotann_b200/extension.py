@@ -57,9 +57,49 @@ def _traverse_checks(output_I, output_D, storage, query, initial_I, initial_D, n
     _require(n_neighbors % 32 == 0, "n_neighbors % WARP_SIZE == 0")
 
 
+# ---- packed form of a caller's CSR tensors, remembered between calls ---------
+# ``traverse_cuda`` takes upstream's tensors as they are.  A caller that passes
+# the SAME tensor objects again (upstream's layers and ``pipeline`` do: the
+# sub-graph lives on the device for the life of the index) gets them packed once,
+# on the second call, and searched in the packed layout from then on: identical
+# results, ~20 % less time per call.  An entry is used only while the three
+# tensor objects are alive and unmodified (torch's version counters); a graph
+# that cannot be packed keeps the CSR path.  PILOTANN_B200_PACK_CACHE=0 turns
+# this off.
+_PACK_CACHE_SLOTS = 2
+_pack_cache: dict = {}
+
+
+def _packed_for(indptr, indices, mapping, n_storage: int, n_neighbors: int):
+    import os
+    import weakref
+    if os.environ.get("PILOTANN_B200_PACK_CACHE", "1") == "0":
+        return None
+    key = (indptr.data_ptr(), indices.data_ptr(), mapping.data_ptr(), indptr.numel(),
+           indices.numel(), n_storage, n_neighbors, indptr.device.index)
+    stamp = (indptr._version, indices._version, mapping._version)
+    entry = _pack_cache.get(key)
+    alive = entry is not None and all(r() is x for r, x in
+                                      zip(entry["refs"], (indptr, indices, mapping)))
+    if not alive or entry["stamp"] != stamp:
+        while len(_pack_cache) >= _PACK_CACHE_SLOTS and key not in _pack_cache:
+            _pack_cache.pop(next(iter(_pack_cache)))
+        _pack_cache[key] = {"refs": tuple(weakref.ref(x) for x in (indptr, indices, mapping)),
+                            "stamp": stamp, "packed": None, "usable": True}
+        return None                      # first sight of these tensors: search them as they are
+    if entry["packed"] is None and entry["usable"]:
+        try:
+            entry["packed"] = pack_graph(indptr, indices, mapping, n_storage, n_neighbors)
+        except RuntimeError:
+            entry["usable"] = False      # e.g. a node with neighbours but no vector row
+    return entry["packed"]
+
+
 def traverse_cuda(output_I, output_D, indptr, indices, mapping, storage, query,
                   initial_I, initial_D, n_neighbors: int, stats=None) -> None:
-    """``extension.traverse_cuda`` (``extension/traverse_cuda.cu:249-315``)."""
+    """``extension.traverse_cuda`` (``extension/traverse_cuda.cu:249-315``).  From the
+    second call with the same graph tensors on, the search runs over their packed
+    form (see ``_packed_for``); results are identical either way."""
     _check_cuda("indptr", indptr, 1, torch.int64)
     _check_cuda("indices", indices, 1, torch.int64)
     _check_cuda("mapping", mapping, 1, torch.int64)
@@ -68,6 +108,11 @@ def traverse_cuda(output_I, output_D, indptr, indices, mapping, storage, query,
     _require(mapping.size(0) == n_nodes, "mapping.size(0) == n_nodes")
     if stats is not None:
         _check_cuda("stats", stats, 2, torch.int32)
+    packed = _packed_for(indptr, indices, mapping, storage.size(0), n_neighbors)
+    if packed is not None:  # same search, same results, over the packed form of these tensors
+        traverse_packed(output_I, output_D, packed[0], packed[1], storage, query, initial_I,
+                        initial_D, n_neighbors, stats=stats)
+        return
     with torch.cuda.device(query.device):
         _C.check(_C.lib().pa_traverse_csr(
             output_I.data_ptr(), output_D.data_ptr(), indptr.data_ptr(), indices.data_ptr(),

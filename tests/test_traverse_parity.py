@@ -156,3 +156,34 @@ def test_repeatable():
     a = run_gpu(p, 64, "packed")
     b = run_gpu(p, 64, "packed")
     assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1]) and torch.equal(a[2], b[2])
+
+
+def test_drop_in_call_switches_to_the_packed_form(oracle_lib):
+    """``traverse_cuda`` with the same graph tensors again: packed on the second
+    call, identical results on every call, CSR again after an in-place change."""
+    from pilotann_b200 import extension
+    p = make_problem(n=3000, d=64, batch=32, ratio=0.5, seed=77)
+    c = to_cuda(p)
+    want = run_oracle(oracle_lib, p, 48)
+    extension._pack_cache.clear()
+    outs = []
+    for call in range(3):
+        oI = torch.full((32, 4, 48), -7, dtype=torch.int64, device="cuda")
+        oD = torch.full((32, 4, 48), -7.0, device="cuda")
+        st = torch.zeros(32, 4, dtype=torch.int32, device="cuda")
+        extension.traverse_cuda(oI, oD, c["indptr"], c["indices"], c["mapping"], c["storage"],
+                                c["query"], c["initial_I"], c["initial_D"], 32, stats=st)
+        torch.cuda.synchronize()
+        outs.append((oI.cpu(), oD.cpu(), st.cpu()))
+        entry = next(iter(extension._pack_cache.values()))
+        assert (entry["packed"] is not None) == (call >= 1)
+    for got in outs:
+        assert_same(got, want)
+    c["indices"].add_(0)                       # in-place op: version counter moves
+    oI = torch.empty(32, 4, 48, dtype=torch.int64, device="cuda")
+    oD = torch.empty(32, 4, 48, device="cuda")
+    extension.traverse_cuda(oI, oD, c["indptr"], c["indices"], c["mapping"], c["storage"],
+                            c["query"], c["initial_I"], c["initial_D"], 32)
+    assert next(iter(extension._pack_cache.values()))["packed"] is None
+    torch.cuda.synchronize()
+    assert torch.equal(oI.cpu(), want[0])
