@@ -58,25 +58,38 @@ def test_traversal_vs_upstream_kernel(ref_ext, law, d, ratio, ef):
     p = make_problem(n=20000, d=d, ratio=ratio, batch=512, n_init=64, seed=21, law=law,
                      build_device="cuda")
     c = to_cuda(p)
-    theirs = _theirs(ref_ext, c, ef, 32)
-    theirs_again = _theirs(ref_ext, c, ef, 32)
-    t_top = topk_ids(*theirs, k)
-    jitter = sum(a != b for a, b in zip(t_top, topk_ids(*theirs_again, k))) / len(t_top)
+    # Upstream's kernel is racy: its own runs disagree with each other.  Five runs
+    # give its run-to-run mismatch rate (mean over the ten pairs); the deterministic
+    # kernel must look like one more such run: its mean mismatch against the five
+    # stays within that rate plus four standard deviations of a rate estimated on
+    # this many queries (plus 0.01 of slack, and never less than the 0.5 % gate).
+    runs = [_theirs(ref_ext, c, ef, 32) for _ in range(5)]
+    tops = [topk_ids(*r, k) for r in runs]
+    n_q = len(tops[0])
+
+    def mismatch(a, b):
+        return sum(x != y for x, y in zip(a, b)) / n_q
+
+    pairs = [(i, j) for i in range(5) for j in range(i + 1, 5)]
+    jitter = sum(mismatch(tops[i], tops[j]) for i, j in pairs) / len(pairs)
+    sigma = (max(jitter, 0.002) * (1.0 - jitter) / n_q) ** 0.5
+    theirs, t_top = runs[0], tops[0]
     truth = p["nodelist"][__import__("pilotann_b200").utils.ground_truth(
         p["query"], p["full"][p["nodelist"]], k)].tolist()
+    t_recall = sum(_recall(tp, truth) for tp in tops) / 5
     for packed in (False, True):
         ours = _ours(c, ef, 32, packed)
         o_top = topk_ids(*ours, k)
-        same = sum(a == b for a, b in zip(o_top, t_top)) / len(t_top)
-        print(f"{law} d={d} ef={ef} packed={packed}: identical top-{k} {same:.4f} "
-              f"(upstream run-to-run mismatch {jitter:.4f})")
-        assert 1.0 - same <= max(0.005, 1.25 * jitter + 0.01)
+        miss = sum(mismatch(o_top, tp) for tp in tops) / 5
+        print(f"{law} d={d} ef={ef} packed={packed}: mismatch against upstream {miss:.4f} "
+              f"(upstream run-to-run {jitter:.4f}, sigma {sigma:.4f})")
+        assert miss <= max(0.005, jitter + 4.0 * sigma + 0.01)
         # recall: never worse than upstream beyond +-0.002 (+ upstream's own noise: a
         # query whose top-k differs typically differs in about one of its k ids).  It
         # may be better by up to the mismatch rate: upstream's races insert some nodes
         # twice, which costs it heap slots and recall; the fixed schedule does not.
-        delta = _recall(o_top, truth) - _recall(t_top, truth)
-        assert -(0.002 + jitter / k) <= delta <= 0.002 + jitter
+        delta = _recall(o_top, truth) - t_recall
+        assert -(0.002 + (jitter + 4.0 * sigma) / k) <= delta <= 0.002 + jitter + 4.0 * sigma
         # distances of ids both sides report, within 1e-5 relative
         for b in range(0, len(t_top), 17):
             mine = dict(zip(ours[0][b].flatten().tolist(), ours[1][b].flatten().tolist()))
@@ -146,14 +159,27 @@ def test_pipeline_drop_in_vs_upstream_pipeline(ref_ext):
     ours_I, ours_D = kernels.pipeline(graph=graph, subgraph=subgraph, subgraph_cuda=sub_cuda,
                                       n_neighbors=32, k=k, ef_search=ef, d_principle=d_p,
                                       chunk_size=chunk, refine=ref_ext.traverse_refine, **args)
-    theirs_I, theirs_D = ref_ext.pipeline(graph, subgraph, sub_cuda, args["storage"],
-                                          args["storage_cuda"], args["query"], args["query_cuda"],
-                                          args["initial_I"], args["initial_D"], 32, ef, d_p, k, chunk)
+    def upstream():
+        return ref_ext.pipeline(graph, subgraph, sub_cuda, args["storage"], args["storage_cuda"],
+                                args["query"], args["query_cuda"], args["initial_I"],
+                                args["initial_D"], 32, ef, d_p, k, chunk)
+
+    def mismatch(a, b):
+        return 1.0 - (a.sort(dim=1).values == b.sort(dim=1).values).all(dim=1).float().mean().item()
+
+    # upstream's GPU half is racy: four runs give its own run-to-run mismatch; this
+    # stage must look like one more run (see test_traversal_vs_upstream_kernel)
+    theirs = [upstream()[0] for _ in range(4)]
+    pairs = [(i, j) for i in range(4) for j in range(i + 1, 4)]
+    jitter = sum(mismatch(theirs[i], theirs[j]) for i, j in pairs) / len(pairs)
+    sigma = (max(jitter, 0.002) * (1.0 - jitter) / ours_I.size(0)) ** 0.5
+    miss = sum(mismatch(ours_I, th) for th in theirs) / 4
     truth = utils.ground_truth(p["query"], p["full"], k)
-    r_ours, r_theirs = utils.recall(ours_I, truth), utils.recall(theirs_I, truth)
-    same = (ours_I.sort(dim=1).values == theirs_I.sort(dim=1).values).all(dim=1).float().mean()
-    print(f"pipeline recall ours {r_ours:.4f} upstream {r_theirs:.4f}, identical top-{k} {same:.4f}")
+    r_ours = utils.recall(ours_I, truth)
+    r_theirs = sum(utils.recall(th, truth) for th in theirs) / 4
+    print(f"pipeline recall ours {r_ours:.4f} upstream {r_theirs:.4f}, top-{k} mismatch {miss:.4f} "
+          f"(upstream run-to-run {jitter:.4f}, sigma {sigma:.4f})")
     assert abs(r_ours - r_theirs) <= 0.005
-    assert same.item() >= 0.97
+    assert miss <= max(0.005, jitter + 4.0 * sigma + 0.01)
     exact = torch.cdist(p["query"].unsqueeze(1), p["full"][ours_I]).squeeze(1).square()
     assert torch.allclose(ours_D, exact, atol=1e-3)
