@@ -541,6 +541,7 @@ traverse_kernel(Layout L, int64_t *__restrict__ out_I, float *__restrict__ out_D
         int64_t u_lo = 0;
         int u_len = 0;
         bool pending = true;
+        bool deferred = false;  // warp 0: the popped root of this group's heap is still in place
         for (int outer = 0; outer <= H + 1; ++outer) {  // more than one pass only if a
                                                         // sampled node has an empty row
             if (w == 0) {
@@ -551,8 +552,6 @@ traverse_kernel(Layout L, int64_t *__restrict__ out_I, float *__restrict__ out_D
                 for (int guard = 0; guard <= H + 1 && __any_sync(kFull, pending); ++guard) {
                     const float top_k = okey[0];
                     const int2 top_v = oval[0];
-                    group_sink<H, W, true>(okey, oval, o_sb, o_lb, gc, pending, CUDART_INF_F,
-                                           make_int2(-1, -1));
                     // written as selects: the groups of the warp disagree on all of
                     // these conditions, and a branch on them would split the warp
                     const bool stop = top_v.x < 0 || top_k >= bound;  // the beam gives up
@@ -567,6 +566,15 @@ traverse_kernel(Layout L, int64_t *__restrict__ out_I, float *__restrict__ out_D
                         usable = lo != hi;
                     }
                     const bool settle = pending && (stop || usable);
+                    // The root is known; removing it from the heap (the sink) can wait
+                    // when this pop settles every pending beam, which is the usual
+                    // case: the popped nodes are published first and the heaps are
+                    // repaired while the neighbour rows are on their way.
+                    if (__any_sync(kFull, pending && !settle))
+                        group_sink<H, W, true>(okey, oval, o_sb, o_lb, gc, pending, CUDART_INF_F,
+                                               make_int2(-1, -1));
+                    else
+                        deferred = pending;
                     u_node = settle ? (stop ? -1 : top_v.x) : u_node;
                     u_row = settle ? (stop ? -1 : top_v.y) : u_row;
                     u_lo = (settle && !stop) ? lo : u_lo;
@@ -584,17 +592,24 @@ traverse_kernel(Layout L, int64_t *__restrict__ out_I, float *__restrict__ out_D
                 again_s[(outer + 1) & 1] = 0;
             }
             __syncthreads();
-            if (pop_s[w].fetch) {  // warp w serves beam w
-                const int32_t node_b = pop_s[w].node;
-                if constexpr (Layout::kPacked) {
-                    // ids, rows and ready-made probes in one 16-byte load per lane
-                    const int32_t row_b = pop_s[w].row;
-                    int4 e[CH];
+            const bool fetch_w = pop_s[w].fetch;  // warp w serves beam w
+            const int32_t node_b = pop_s[w].node;
+            if constexpr (Layout::kPacked) {
+                // ids, rows and ready-made probes in one 16-byte load per lane
+                const int32_t row_b = pop_s[w].row;
+                int4 e[CH];
 #pragma unroll
-                    for (int c = 0; c < CH; ++c)
-                        e[c] = node_b >= 0
-                            ? __ldg(L.nbr + static_cast<int64_t>(row_b) * n_nb + 32 * c + lane)
-                            : make_int4(-1, -1, 0, 0);
+                for (int c = 0; c < CH; ++c)
+                    e[c] = (fetch_w && node_b >= 0)
+                        ? __ldg(L.nbr + static_cast<int64_t>(row_b) * n_nb + 32 * c + lane)
+                        : make_int4(-1, -1, 0, 0);
+                // the open warp repairs its heaps while its row is on its way
+                if (w == 0 && __any_sync(kFull, deferred)) {
+                    group_sink<H, W, true>(okey, oval, o_sb, o_lb, gc, deferred, CUDART_INF_F,
+                                           make_int2(-1, -1));
+                    deferred = false;
+                }
+                if (fetch_w) {
                     // a sampled node whose adjacency row is empty: its beam pops again
                     if (node_b >= 0 && __shfl_sync(kFull, e[0].x, 0) == kEmptyRowTag) {
                         if (lane == 0) atomicOr(&again_s[outer & 1], 1u << w);
@@ -607,7 +622,14 @@ traverse_kernel(Layout L, int64_t *__restrict__ out_I, float *__restrict__ out_D
                                                       static_cast<uint32_t>(e[c].w));
                         }
                     }
-                } else {
+                }
+            } else {
+                if (w == 0 && __any_sync(kFull, deferred)) {
+                    group_sink<H, W, true>(okey, oval, o_sb, o_lb, gc, deferred, CUDART_INF_F,
+                                           make_int2(-1, -1));
+                    deferred = false;
+                }
+                if (fetch_w) {
                     const int64_t lo_b = pop_s[w].lo;
                     const int len_b = pop_s[w].len;
 #pragma unroll
