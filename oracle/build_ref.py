@@ -1,7 +1,7 @@
 """Compile the upstream PilotANN extension, unmodified, into ``oracle/_ref/``.
 
 TEST INFRASTRUCTURE ONLY.  The upstream sources are compiled where they lie
-(``$PILOTANN_REFERENCE`` or ``/root/reference``); nothing is copied into this
+(the checkout named by ``$PILOTANN_REFERENCE``, or the default one); nothing is copied into this
 repository and the upstream build system (``setup.py``) is not run: this file
 is the whole recipe -- one ``g++``/``nvcc`` command per translation unit listed
 in the upstream ``setup.py:28-37`` and one link step.  The host flags are the
