@@ -78,6 +78,8 @@ def _packed_for(indptr, indices, mapping, n_storage: int, n_neighbors: int):
     key = (indptr.data_ptr(), indices.data_ptr(), mapping.data_ptr(), indptr.numel(),
            indices.numel(), n_storage, n_neighbors, indptr.device.index)
     stamp = (indptr._version, indices._version, mapping._version)
+    for dead in [k for k, e in _pack_cache.items() if any(r() is None for r in e["refs"])]:
+        del _pack_cache[dead]            # the caller's tensors are gone: free their packed form
     entry = _pack_cache.get(key)
     alive = entry is not None and all(r() is x for r, x in
                                       zip(entry["refs"], (indptr, indices, mapping)))
