@@ -271,8 +271,35 @@ def cpu_baseline_leg(w, index, queries, truth, ef_gpu, repeats=3):
                                "refine_qps": round(q.size(0) / dt, 1)})
             if e == ef_gpu:
                 pipe = pipe_sweep[-1]
+    # upstream's own CUDA traversal kernel on this GPU, same tensors, same entries, at
+    # the operating ef: the recompiled-reference number the kernel here is held against
+    upstream_ms = None
+    if ref is not None and index.stage is not None and hasattr(ref, "traverse_cuda"):
+        try:
+            dev = index.storage_cuda.device
+            red = rotated[:, :w.d_principle].contiguous().to(dev)
+            eI, eD = index.entry.search(red)
+            oI = torch.empty(q.size(0), 4, ef_gpu, dtype=torch.int64, device=dev)
+            oD = torch.empty(q.size(0), 4, ef_gpu, dtype=torch.float32, device=dev)
+            flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+            samples = []
+            for i in range(6):
+                flush.zero_()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                ref.traverse_cuda(oI, oD, index.subgraph_cuda.indptr, index.subgraph_cuda.indices,
+                                  index.mapping_cuda, index.storage_cuda, red, eI, eD,
+                                  index.n_neighbors)
+                b.record()
+                torch.cuda.synchronize(dev)
+                if i >= 3:
+                    samples.append(a.elapsed_time(b))
+            upstream_ms = round(statistics.median(samples), 4)
+        except Exception as exc:                     # a reported extra, never fatal
+            upstream_ms = f"unavailable: {exc}"
     chosen = best or (sweep[-1] if sweep else {"ef": None, "recall": None, "qps": None})
-    return {"value": chosen["qps"], "unit": "queries/s", "cores": threads, "kind": kind,
+    return {"upstream_cuda_kernel_ms": upstream_ms,
+            "value": chosen["qps"], "unit": "queries/s", "cores": threads, "kind": kind,
             "sample": f"{q.size(0)} queries, upstream traverse_cpu on the full graph, ef sweep "
                       f"until recall@{k}>={TARGET_RECALL}, median of {repeats}",
             "ef": chosen["ef"], "recall": chosen["recall"], "sweep": sweep, "pipeline": pipe,
