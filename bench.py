@@ -306,6 +306,96 @@ def cpu_baseline_leg(w, index, queries, truth, ef_gpu, repeats=3):
             "pipeline_sweep": pipe_sweep}
 
 
+# ------------------------------------------------------------------- parity
+
+def _top_ids(I: torch.Tensor, D: torch.Tensor, k: int) -> torch.Tensor:
+    """Final top-k ids per query of a [B, 4, ef] candidate buffer by (distance, id),
+    duplicates and pads dropped; returned sorted by id so that rows compare as sets."""
+    B = I.size(0)
+    I = I.reshape(B, -1).cpu()
+    D = D.reshape(B, -1).cpu().clone()
+    order = torch.argsort(I, dim=1, stable=True)
+    I, D = torch.gather(I, 1, order), torch.gather(D, 1, order)
+    dup = torch.zeros_like(I, dtype=torch.bool)
+    dup[:, 1:] = I[:, 1:] == I[:, :-1]
+    D[(I < 0) | dup] = float("inf")
+    order = torch.argsort(D, dim=1, stable=True)[:, :k]
+    return torch.gather(I, 1, order).sort(dim=1).values
+
+
+def parity_leg(w, index, red, EP_I, EP_D, out_I, out_D, stats, ef, runs=5):
+    """Parity record on the benchmark's own index, queries and entries: this
+    kernel against the CPU oracle (bit for bit) and against upstream's CUDA
+    kernels compiled for this GPU (upstream's traversal is racy, so its runs are
+    compared with each other first)."""
+    import oracle
+    k = w.top_k
+    dev = red.device
+    torch.cuda.synchronize(dev)
+    rec = {"queries": int(red.size(0)), "ef_search": ef, "top_k": k}
+    t0 = time.perf_counter()
+    wI, wD, wS = oracle.traverse(index.subgraph.indptr, index.subgraph.indices, index.mapping,
+                                 index.storage_cuda.cpu(), red.cpu(), EP_I.cpu(), EP_D.cpu(),
+                                 index.n_neighbors, ef, with_stats=True)
+    ids_ok = torch.equal(out_I.cpu(), wI)
+    dist_ok = torch.equal(out_D.cpu().view(torch.int32), wD.view(torch.int32))
+    stats_ok = torch.equal(stats.cpu(), wS)
+    rec["oracle_bit_exact"] = bool(ids_ok and dist_ok and stats_ok)
+    rec["oracle"] = {"ids": ids_ok, "distance_bits": dist_ok,
+                     "stats_rounds_expansions_evaluations_bloombits": stats_ok,
+                     "seconds": round(time.perf_counter() - t0, 1)}
+    ref = load_reference()
+    if ref is None or not hasattr(ref, "traverse_cuda"):
+        rec["upstream"] = "unavailable: upstream module not built"
+        return rec
+    ours_top = _top_ids(out_I, out_D, k)
+    if index.entry.route_vectors is not None:
+        from pilotann_b200 import extension
+        our_router = extension.routing_cuda(red, index.entry.route_vectors,
+                                            index.entry.entry_nodes, index.entry.entry_vectors)[0]
+        their_router, their_leaf = ref.routing_cuda(red, index.entry.route_vectors,
+                                                    index.entry.entry_nodes,
+                                                    index.entry.entry_vectors)
+        torch.cuda.synchronize(dev)
+        rec["router_ids_differ_from_upstream"] = int((our_router != their_router).sum())
+        rec["max_rel_leaf_distance_err"] = float(
+            ((EP_D - their_leaf).abs() / their_leaf.abs().clamp_min(1e-30)).max())
+    tops, first = [], None
+    for _ in range(runs):
+        tI = torch.empty_like(out_I)
+        tD = torch.empty_like(out_D)
+        ref.traverse_cuda(tI, tD, index.subgraph_cuda.indptr, index.subgraph_cuda.indices,
+                          index.mapping_cuda, index.storage_cuda, red, EP_I, EP_D,
+                          index.n_neighbors)
+        torch.cuda.synchronize(dev)
+        tops.append(_top_ids(tI, tD, k))
+        if first is None:
+            first = (tI.cpu(), tD.cpu())
+
+    def mismatch(a, b):
+        return float((a != b).any(dim=1).float().mean())
+
+    pairs = [(i, j) for i in range(runs) for j in range(i + 1, runs)]
+    jitter = sum(mismatch(tops[i], tops[j]) for i, j in pairs) / len(pairs)
+    miss = sum(mismatch(ours_top, t) for t in tops) / runs
+    rec["top%d_mismatch_vs_upstream" % k] = round(miss, 5)
+    rec["upstream_run_to_run"] = round(jitter, 5)
+    rec["gate"] = "mismatch <= max(0.005, upstream_run_to_run): " + (
+        "met" if miss <= max(0.005, jitter) else
+        "NOT met" if jitter == 0 else "above upstream's own rate (limited by the reference: "
+        "its traversal does not reproduce itself)")
+    # distances of ids both sides report
+    oI, oD = out_I.cpu().reshape(red.size(0), -1), out_D.cpu().reshape(red.size(0), -1)
+    worst = 0.0
+    for b in range(0, red.size(0), 8):
+        mine = dict(zip(oI[b].tolist(), oD[b].tolist()))
+        for i, dist in zip(first[0][b].flatten().tolist(), first[1][b].flatten().tolist()):
+            if i >= 0 and i in mine and dist > 0:
+                worst = max(worst, abs(mine[i] - dist) / dist)
+    rec["max_rel_distance_err"] = worst
+    return rec
+
+
 # ---------------------------------------------------------------------- main
 
 def flush_l2(buf):
@@ -487,6 +577,7 @@ def main():
                      "expansions_per_query": E / B, "evaluations_per_query": C / B},
     }
     if world == 1 and not args.no_cpu:
+        line["parity"] = parity_leg(w, index, red, EP_I, EP_D, out_I, out_D, stats, ef)
         line["cpu_baseline"] = cpu_baseline_leg(w, index, queries, truth, ef)
     if world > 1:
         torch.distributed.destroy_process_group()

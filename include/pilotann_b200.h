@@ -130,6 +130,14 @@ int pa_project(float *out, const float *query, const float *VT, int64_t batch,
  * then undefined), or PA_ERR_CUDA.  No upstream counterpart. */
 int pa_device_status(int reset);
 
+/* Diagnostic for the bounded waits: launches one thread that polls 16 times on an
+ * mbarrier phase nothing completes, gives up, and sets the status word the way a
+ * tensor-core kernel of this library does when a copy never lands.  Afterwards
+ * pa_device_status(1) returns 1 and the device is as usable as before.  While the
+ * word is set, entry routing ignores tensor-core router scores and measures every
+ * router exactly.  No upstream counterpart. */
+int pa_selftest_bounded_wait(void *stream);
+
 /* ---- search stage object -------------------------------------------------
  * Replaces the GPU half of `pipeline` (extension/pipeline_cpu.cpp:32-145): its
  * static stream pool (:67-75), the per-call device and pinned handoff buffers

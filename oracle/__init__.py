@@ -40,6 +40,10 @@ def lib() -> ctypes.CDLL:
         L.po_heap_pushpop.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int,
                                       ctypes.c_float, ctypes.c_int64]
         L.po_heap_replace.argtypes = L.po_heap_pushpop.argtypes
+        L.po_warp_distance.restype = ctypes.c_float
+        L.po_warp_distance.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int,
+                                       ctypes.c_int]
+        L.po_cpu_heap_size_for.restype = ctypes.c_int
         _lib = L
     return _lib
 
@@ -183,3 +187,42 @@ def refine(buffer_I, buffer_D, subgraph, fullgraph, storage, query, k: int, ef_s
     if rc != 0:
         raise RuntimeError("oracle: ef_search not supported")
     return out_I, out_D
+
+
+def warp_distance(query: torch.Tensor, row: torch.Tensor, offset: int = 0) -> float:
+    """Squared distance over dims [offset, d) in the summation order of the GPU
+    refinement kernel (32 lanes x float4 stripes, butterfly reduction)."""
+    _chk(row, torch.float32, 1), _chk(query, torch.float32, 1)
+    return float(lib().po_warp_distance(_p(query), _p(row), row.numel(), offset))
+
+
+def cpu_heap_size_for(ef: int) -> int:
+    """Heap capacity of the CPU consumer (``traverse_cpu.cpp:228-254``)."""
+    return int(lib().po_cpu_heap_size_for(ctypes.c_int(ef)))
+
+
+def refine_ex(buffer_I, buffer_D, subgraph, fullgraph, storage, query, k: int, ef_search: int,
+              d_principle: int, gpu_order: bool = True, stages: int = 3,
+              with_stats: bool = False):
+    """``traverse_refine`` restated with a choice of summation order
+    (``gpu_order``: the refinement kernel's, else upstream's AVX2 one) and of
+    stages (2: sub-graph stage only, the buffer is rewritten in place and no top-k
+    is produced; 3: both).  Returns ``(out_I, out_D[, stats int32 [B,4]])``."""
+    _chk(buffer_I, torch.int64, 2), _chk(buffer_D, torch.float32, 2)
+    _chk(storage, torch.float32, 2), _chk(query, torch.float32, 2)
+    for g in (*subgraph, *fullgraph):
+        _chk(g, torch.int64, 1)
+    B, d = query.shape
+    out_I = torch.full((B, k), -1, dtype=torch.int64)
+    out_D = torch.zeros(B, k, dtype=torch.float32)
+    stats = torch.zeros(B, 4, dtype=torch.int32) if with_stats else None
+    rc = lib().po_refine_ex(_p(out_I), _p(out_D), _p(buffer_I), _p(buffer_D), _p(subgraph[0]),
+                            _p(subgraph[1]), _p(fullgraph[0]), _p(fullgraph[1]), _p(storage),
+                            _p(query), ctypes.c_int64(B), ctypes.c_int64(storage.size(0)),
+                            ctypes.c_int(d), ctypes.c_int(d_principle),
+                            ctypes.c_int(buffer_I.size(1)), ctypes.c_int(k),
+                            ctypes.c_int(ef_search), ctypes.c_int(1 if gpu_order else 0),
+                            ctypes.c_int(stages), _p(stats))
+    if rc != 0:
+        raise RuntimeError("oracle: ef_search not supported")
+    return (out_I, out_D, stats) if with_stats else (out_I, out_D)

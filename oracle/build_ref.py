@@ -1,7 +1,8 @@
 """Compile the upstream PilotANN extension, unmodified, into ``oracle/_ref/``.
 
 TEST INFRASTRUCTURE ONLY.  The upstream sources are compiled where they lie
-(the checkout named by ``$PILOTANN_REFERENCE``, or the default one); nothing is copied into this
+(the checkout named by ``$PILOTANN_REFERENCE``, else a ``reference`` directory beside this
+repository); nothing is copied into this
 repository and the upstream build system (``setup.py``) is not run: this file
 is the whole recipe -- one ``g++``/``nvcc`` command per translation unit listed
 in the upstream ``setup.py:28-37`` and one link step.  The host flags are the
@@ -37,7 +38,7 @@ SOURCES = [
 
 
 def reference_root() -> Path | None:
-    root = Path(os.environ.get("PILOTANN_REFERENCE", "/root/reference"))
+    root = Path(os.environ.get("PILOTANN_REFERENCE", HERE.parent.parent / "reference"))
     return root if (root / "extension" / "entry.cpp").is_file() else None
 
 

@@ -18,6 +18,11 @@
  *   po_project                         pilot_ann/layers/staged.py:198
  *   po_search_cpu / po_refine          extension/traverse_cpu.cpp:12-163, 167-257,
  *                                      261-369 (the CPU consumer of the handoff)
+ *   po_refine_ex                       the same two stages with the summation
+ *                                      order of the GPU refinement kernel
+ *                                      (po_warp_distance) instead of the AVX2 one,
+ *                                      so that kernel can be compared bit for bit;
+ *                                      stage 2 alone or stages 2 + 3
  *
  * The upstream GPU kernel is racy (four warps race on the bloom filter, all 32
  * lanes of a warp redundantly run the heap code).  This restatement fixes ONE
@@ -389,20 +394,52 @@ static float dist_avx_order(const float *q, const float *x, int d, int offset) {
 
 /* traverse_cpu.cpp:12-163.  `visited` is the epoch-marker array of
  * bitmask.hpp:12-45 (int32 per node, value == marker means visited). */
+/* Summation order of the GPU refinement kernel: 32 lanes, lane t owns floats
+ * [offset + 128m + 4t, +4); per stripe acc += fma(dx,dx,dy*dy); acc +=
+ * fma(dz,dz,dw*dw) in ascending m; then the butterfly 16, 8, 4, 2, 1 (lane 0 of a
+ * shuffle-xor butterfly adds in exactly this order, and every lane ends with the
+ * same bits because the additions commute). */
+float po_warp_distance(const float *q, const float *x, int d, int offset) {
+    float lane[32];
+    for (int t = 0; t < 32; t++) {
+        float acc = 0.0f;
+        for (int o = offset + 4 * t; o < d; o += 128) {
+            float dx = q[o] - x[o], dy = q[o + 1] - x[o + 1];
+            float dz = q[o + 2] - x[o + 2], dw = q[o + 3] - x[o + 3];
+            acc = acc + fmaf(dx, dx, dy * dy);
+            acc = acc + fmaf(dz, dz, dw * dw);
+        }
+        lane[t] = acc;
+    }
+    for (int off = 16; off > 0; off /= 2)
+        for (int t = 0; t < off; t++) lane[t] = lane[t] + lane[t + off];
+    return lane[0];
+}
+
+static float full_dist(const float *q, const float *x, int d, int offset, int dist_mode) {
+    return dist_mode ? po_warp_distance(q, x, d, offset) : dist_avx_order(q, x, d, offset);
+}
+
+/* traverse_cpu.cpp:12-163.  `visited` is the epoch-marker array of
+ * bitmask.hpp:12-45 (int32 per node, value == marker means visited).
+ * dist_mode 0: AVX2 summation order (the one pinned to upstream); 1: the GPU
+ * kernel's.  stats (optional, 2 ints): nodes expanded, distance evaluations. */
 static void search_cpu_one(int64_t *out_I, float *out_D, int32_t *visited,
                            int64_t *init_I, float *init_D, const int64_t *indptr,
                            const int64_t *indices, const float *storage,
                            const float *query, int d, int d_principle, int n_init,
-                           int ef, int k, int H, int32_t marker, int max_iter) {
+                           int ef, int k, int H, int32_t marker, int max_iter,
+                           int dist_mode, int32_t *stats) {
     float *buf_D = malloc(sizeof(float) * 3 * H);
     int64_t *buf_I = malloc(sizeof(int64_t) * 3 * H);
     float *open_D = buf_D + H;
     int64_t *open_I = buf_I + H;
+    int32_t n_expand = 0, n_eval = 0;
     if (d_principle < d) /* :41-62 residual over the trailing dims, in place */
         for (int i = 0; i < n_init; i++)
             if (init_I[i] >= 0)
-                init_D[i] += dist_avx_order(query, storage + init_I[i] * (int64_t)d,
-                                            d, d_principle);
+                init_D[i] += full_dist(query, storage + init_I[i] * (int64_t)d, d,
+                                       d_principle, dist_mode);
     for (int i = 0; i < H; i++) { buf_D[i] = -INFINITY; buf_I[i] = -1; }
     for (int i = 0; i < 2 * H; i++) { open_D[i] = INFINITY; open_I[i] = -1; }
     for (int i = 0; i < n_init; i++) { /* :69-79 */
@@ -416,12 +453,14 @@ static void search_cpu_one(int64_t *out_I, float *out_D, int32_t *visited,
         float key; int64_t u;
         po_heap_pop(open_D, open_I, 2 * H, &key, &u);
         if (u < 0 || key >= -buf_D[0]) break;
+        n_expand++;
         for (int64_t i = indptr[u]; i < indptr[u + 1]; i++) { /* :105-135 */
             int64_t v = indices[i];
             if (v < 0) break;
             if (visited[v] == -1 || visited[v] == marker) continue;
             visited[v] = marker;
-            float dist = dist_avx_order(query, storage + v * (int64_t)d, d, 0);
+            float dist = full_dist(query, storage + v * (int64_t)d, d, 0, dist_mode);
+            n_eval++;
             if (dist >= -buf_D[0]) continue; /* :27-29 */
             po_heap_pushpop(buf_D, buf_I, H, -dist, v);
             po_heap_replace(open_D, open_I, 2 * H, dist, v);
@@ -436,6 +475,7 @@ static void search_cpu_one(int64_t *out_I, float *out_D, int32_t *visited,
         out_I[k - i - 1] = val;
         out_D[k - i - 1] = -key;
     }
+    if (stats) { stats[0] = n_expand; stats[1] = n_eval; }
     free(buf_D);
     free(buf_I);
 }
@@ -464,21 +504,27 @@ int po_search_cpu(int64_t *out_I, float *out_D, int64_t *init_I, float *init_D,
             marker++;
             search_cpu_one(out_I + b * k, out_D + b * k, visited, init_I + b * n_init,
                            init_D + b * n_init, indptr, indices, storage,
-                           query + b * d, d, d, n_init, ef, k, H, marker, 1024);
+                           query + b * d, d, d, n_init, ef, k, H, marker, 1024, 0, NULL);
         }
         free(visited);
     }
     return 0;
 }
 
+int po_cpu_heap_size_for(int ef) { return cpu_heap_size_for(ef); }
+
 /* traverse_cpu.cpp:261-369: stage 2 (subgraph, residual fix-up, two expansion
  * steps, result written back into the handoff buffer) then stage 3 (full
- * graph).  buffer_* [B,n_buf] is the handoff, read and overwritten. */
-int po_refine(int64_t *out_I, float *out_D, int64_t *buffer_I, float *buffer_D,
-              const int64_t *sub_indptr, const int64_t *sub_indices,
-              const int64_t *full_indptr, const int64_t *full_indices,
-              const float *storage, const float *query, int64_t batch,
-              int64_t n_storage, int d, int d_principle, int n_buf, int k, int ef) {
+ * graph).  buffer_* [B,n_buf] is the handoff, read and overwritten.
+ * dist_mode: see search_cpu_one.  stages: 2 = stage 2 only (out_* untouched),
+ * 3 = both.  stats: NULL or int32 [B,4] = stage-2 expansions, stage-2
+ * evaluations, stage-3 expansions, stage-3 evaluations. */
+int po_refine_ex(int64_t *out_I, float *out_D, int64_t *buffer_I, float *buffer_D,
+                 const int64_t *sub_indptr, const int64_t *sub_indices,
+                 const int64_t *full_indptr, const int64_t *full_indices,
+                 const float *storage, const float *query, int64_t batch,
+                 int64_t n_storage, int d, int d_principle, int n_buf, int k, int ef,
+                 int dist_mode, int stages, int32_t *stats) {
     int H = cpu_heap_size_for(ef);
     if (H < 0) return -1;
 #pragma omp parallel
@@ -490,6 +536,7 @@ int po_refine(int64_t *out_I, float *out_D, int64_t *buffer_I, float *buffer_D,
             marker++;
             int64_t *bI = buffer_I + b * n_buf;
             float *bD = buffer_D + b * n_buf;
+            int32_t st[4] = {0, 0, 0, 0};
             /* the stage-2 call reads and writes the same rows (pipeline_cpu.cpp:
              * 110-114 passes one tensor as both); snapshot the inputs first so
              * that the write-back cannot disturb them */
@@ -498,14 +545,27 @@ int po_refine(int64_t *out_I, float *out_D, int64_t *buffer_I, float *buffer_D,
             memcpy(tI, bI, sizeof(int64_t) * n_buf);
             memcpy(tD, bD, sizeof(float) * n_buf);
             search_cpu_one(bI, bD, visited, tI, tD, sub_indptr, sub_indices, storage,
-                           query + b * d, d, d_principle, n_buf, ef, n_buf, H, marker, 2);
-            search_cpu_one(out_I + b * k, out_D + b * k, visited, bI, bD, full_indptr,
-                           full_indices, storage, query + b * d, d, d, n_buf, ef, k, H,
-                           marker, 1024);
+                           query + b * d, d, d_principle, n_buf, ef, n_buf, H, marker, 2,
+                           dist_mode, st);
+            if (stages >= 3)
+                search_cpu_one(out_I + b * k, out_D + b * k, visited, bI, bD, full_indptr,
+                               full_indices, storage, query + b * d, d, d, n_buf, ef, k, H,
+                               marker, 1024, dist_mode, st + 2);
+            if (stats) memcpy(stats + 4 * b, st, sizeof st);
             free(tI);
             free(tD);
         }
         free(visited);
     }
     return 0;
+}
+
+int po_refine(int64_t *out_I, float *out_D, int64_t *buffer_I, float *buffer_D,
+              const int64_t *sub_indptr, const int64_t *sub_indices,
+              const int64_t *full_indptr, const int64_t *full_indices,
+              const float *storage, const float *query, int64_t batch,
+              int64_t n_storage, int d, int d_principle, int n_buf, int k, int ef) {
+    return po_refine_ex(out_I, out_D, buffer_I, buffer_D, sub_indptr, sub_indices, full_indptr,
+                        full_indices, storage, query, batch, n_storage, d, d_principle, n_buf, k,
+                        ef, 0, 3, NULL);
 }

@@ -21,6 +21,7 @@ SYMBOLS = (
     "pa_traverse_packed", "pa_route", "pa_project", "pa_stage_create", "pa_stage_destroy",
     "pa_stage_search", "pa_stage_search_device", "pa_stage_synchronize", "pa_stage_stream",
     "pa_launch_count", "pa_search_reduced_noalloc", "pa_device_status", "pa_route_ws", "pa_route_workspace_floats",
+    "pa_selftest_bounded_wait",
 )
 
 
@@ -71,6 +72,8 @@ def lib() -> ctypes.CDLL:
     L.pa_stage_stream.argtypes = [P]
     L.pa_stage_stream.restype = P
     L.pa_launch_count.restype = c_int64
+    L.pa_selftest_bounded_wait.argtypes = [P]
+    L.pa_selftest_bounded_wait.restype = c_int
     L.pa_device_status.argtypes = [c_int]
     L.pa_device_status.restype = c_int
     L.pa_search_reduced_noalloc.argtypes = [P, P, P, P, P, P, P, P, P, c_int64, c_int64, c_int64,

@@ -74,8 +74,8 @@ extern "C" int pa_search_reduced_noalloc(
                     PA_NOALLOC_MAX_LEAVES);
     PA_REQUIRE(n_leaves > 0 && n_leaves % 32 == 0, "n_leaves must be a multiple of 32");
     PA_REQUIRE(route_vectors != nullptr ? n_routers > 0 : true, "n_routers must be positive");
-    PA_REQUIRE(d_principle > 0 && d_principle % 4 == 0 && d_principle <= 8192,
-               "d_principle must be a multiple of 4 (at most 8192)");
+    PA_REQUIRE(d_principle > 0 && d_principle % 4 == 0 && d_principle <= 4096,
+               "d_principle must be a multiple of 4 (at most 4096)");
     if (batch == 0) return PA_OK;
     PA_REQUIRE(query && entry_nodes && entry_vectors, "null pointer");
     PA_REQUIRE(aligned16(query) && aligned16(entry_vectors) &&
@@ -83,6 +83,13 @@ extern "C" int pa_search_reduced_noalloc(
                "vectors must be 16-byte aligned");
     unsigned char *scratch = nullptr;
     int rc = scratch_on_current_device(&scratch);
+    if (rc != PA_OK) return rc;
+    // every check of the traversal runs before the routing kernel is enqueued: a
+    // refused call launches nothing
+    rc = traverse_packed_check(output_I, output_D, packed_nbr, row_of, storage, query, d_principle,
+                               reinterpret_cast<const int64_t *>(scratch),
+                               reinterpret_cast<const float *>(scratch), batch, n_nodes,
+                               d_principle, n_neighbors, n_leaves, ef_search);
     if (rc != PA_OK) return rc;
     // layout: ids for MAX_BATCH x MAX_LEAVES first, distances after them; rows are
     // packed at the call's own n_leaves.  Every element the traversal reads is

@@ -34,6 +34,11 @@ int traverse_packed_launch(int64_t *output_I, float *output_D, const int32_t *pa
                            int64_t batch, int64_t n_nodes, int64_t n_storage, int d_model,
                            int n_neighbors, int n_initials, int ef_search, int32_t *stats,
                            cudaStream_t stream);
+int traverse_packed_check(const int64_t *output_I, const float *output_D,
+                          const int32_t *packed_nbr, const int32_t *row_of, const float *storage,
+                          const float *query, int64_t ldq, const int64_t *initial_I,
+                          const float *initial_D, int64_t batch, int64_t n_nodes, int d_model,
+                          int n_neighbors, int n_initials, int ef_search);
 int route_launch(int64_t *router, float *leaf_D, int64_t *leaf_I, const float *query,
                  int64_t ldq, const float *route_vectors, const int64_t *entry_nodes,
                  const float *entry_vectors, int64_t batch, int d, int n_routers, int n_leaves,
@@ -42,6 +47,7 @@ int router_norms_launch(float *rnorm2, const float *route_vectors, int n_routers
                         cudaStream_t stream);
 int gemm_tf32x3_launch(float *out, const float *A, const float *B, int M, int N, int K,
                        int64_t lda, int64_t ldb, int64_t ldo, cudaStream_t stream);
+const int *gemm_status_address();
 int project_launch(float *out, const float *query, const float *VT, int64_t batch, int d,
                    int d_out, int64_t ld_out, cudaStream_t stream);
 

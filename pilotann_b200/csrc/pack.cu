@@ -21,10 +21,10 @@ __global__ void pack_rows_kernel(int4 *__restrict__ nbr, int32_t *__restrict__ r
     const int64_t row = mapping[u];
     const int64_t lo = indptr[u], hi = indptr[u + 1];
     if (lane == 0) row_of[u] = row < 0 ? -1 : static_cast<int32_t>(row);
-    if (row >= n_storage || row > 0x7ffffffe) { if (lane == 0) atomicExch(error, 2); return; }
+    if (row >= n_storage || row > 0x7ffffffe) { if (lane == 0) atomicMax(error, 2); return; }
     if (row < 0) {
         // a node without a vector row cannot carry an adjacency row here
-        if (hi != lo && lane == 0) atomicExch(error, 1);
+        if (hi != lo && lane == 0) atomicMax(error, 1);
         return;
     }
     const int64_t len = min(hi - lo, static_cast<int64_t>(n_nb));
@@ -33,7 +33,7 @@ __global__ void pack_rows_kernel(int4 *__restrict__ nbr, int32_t *__restrict__ r
         int2 e = make_int2(-1, -1);
         if (i < len) {
             int64_t v = indices[lo + i];
-            if (v >= n_nodes) { atomicExch(error, 2); v = -1; }
+            if (v >= n_nodes) { atomicMax(error, 2); v = -1; }
             if (v >= 0) {
                 int64_t r = mapping[v];
                 e = make_int2(static_cast<int32_t>(v), r < 0 ? -1 : static_cast<int32_t>(r));
@@ -60,8 +60,16 @@ extern "C" int pa_pack_graph(int32_t *packed_nbr, int32_t *row_of, const int64_t
     PA_REQUIRE(packed_nbr && row_of && indptr && indices && mapping, "null pointer");
     PA_REQUIRE((reinterpret_cast<uintptr_t>(packed_nbr) & 15u) == 0,
                "packed_nbr must be 16-byte aligned");
-    int *error = nullptr;
-    PA_CUDA_TRY(cudaMallocAsync(&error, sizeof(int), stream));
+    // error word of the row kernel (the more severe code wins); released on every
+    // way out of this function
+    struct ErrorWord {
+        int *p = nullptr;
+        cudaStream_t s;
+        ~ErrorWord() { if (p != nullptr) cudaFreeAsync(p, s); }
+    } word;
+    word.s = stream;
+    PA_CUDA_TRY(cudaMallocAsync(&word.p, sizeof(int), stream));
+    int *error = word.p;
     PA_CUDA_TRY(cudaMemsetAsync(error, 0, sizeof(int), stream));
     const int64_t n_slots = n_storage * n_neighbors;
     if (n_slots > 0) {
@@ -80,7 +88,6 @@ extern "C" int pa_pack_graph(int32_t *packed_nbr, int32_t *row_of, const int64_t
     int host_error = 0;
     PA_CUDA_TRY(cudaMemcpyAsync(&host_error, error, sizeof(int), cudaMemcpyDeviceToHost, stream));
     PA_CUDA_TRY(cudaStreamSynchronize(stream));
-    PA_CUDA_TRY(cudaFreeAsync(error, stream));
     if (host_error == 1)
         return fail(PA_ERR_UNPACKABLE, "a node with neighbours has no storage row (mapping < 0)");
     if (host_error == 2) return fail(PA_ERR_UNPACKABLE, "an id or storage row is out of range");

@@ -248,6 +248,18 @@ gemm_tf32x3_kernel(float *__restrict__ out, const __grid_constant__ CUtensorMap 
     if (warp == 0) tc05::tmem_dealloc(tmem, BN);
 }
 
+// Diagnostic: the give-up path of the GEMM, alone.  One thread waits a handful of
+// polls on an mbarrier phase that nothing completes, records the failure in the
+// status word exactly as the GEMM does, and returns; nothing is left pending.
+__global__ void bounded_wait_selftest_kernel(uint32_t polls) {
+    __shared__ __align__(8) uint64_t bar;
+    if (threadIdx.x == 0) {
+        tc05::mbar_init(tc05::smem_u32(&bar), 1);
+        tc05::fence_barrier_init();
+        if (!tc05::mbar_wait_bounded(tc05::smem_u32(&bar), 0, polls)) atomicExch(&g_gemm_status, 1);
+    }
+}
+
 static bool gemm_operands_ok(const float *A, const float *B, int K, int64_t lda, int64_t ldb) {
     return K % 4 == 0 && lda % 4 == 0 && ldb % 4 == 0 && aligned16(A) && aligned16(B);
 }
@@ -285,6 +297,24 @@ static int make_tile_map(CUtensorMap *map, const float *base, int rows, int K, i
     if (rc != CUDA_SUCCESS)
         return fail(PA_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d)", static_cast<int>(rc));
     return PA_OK;
+}
+
+// Device address of the status word on the current device (nullptr if the lookup
+// fails): kernels that consume a GEMM's output read it to learn that the GEMM gave
+// up.  Looked up once per device.
+const int *gemm_status_address() {
+    static const int *addr[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (addr[dev] == nullptr) {
+        void *p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_gemm_status) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return nullptr;
+        }
+        addr[dev] = static_cast<const int *>(p);
+    }
+    return addr[dev];
 }
 
 int gemm_tf32x3_launch(float *out, const float *A, const float *B, int M, int N, int K,
@@ -336,6 +366,13 @@ extern "C" int pa_project(float *out, const float *query, const float *VT, int64
     PA_REQUIRE(out && query && VT, "null pointer");
     return project_launch(out, query, VT, batch, d_model, d_out, ld_out,
                           static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int pa_selftest_bounded_wait(void *stream) {
+    pa::bounded_wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(16u);
+    pa::count_launch();
+    PA_CUDA_TRY(cudaGetLastError());
+    return PA_OK;
 }
 
 extern "C" int pa_device_status(int reset) {

@@ -1,0 +1,511 @@
+// Refinement of the candidate handoff on the GPU: the two stages upstream runs on
+// the CPU in `traverse_refine` (extension/traverse_cpu.cpp:261-369), each of them
+// one call of `traverse_cpu_kernel` (:12-163):
+//
+//   stage 2  the [batch, 4 * ef] candidates of the reduced-space traversal get
+//            their distances completed over dims d_principle .. d_model (:41-62),
+//            seed a best-first search on the SUB-graph that is cut off after
+//            REFINE_STEP = 2 expansions (:64-136), and the best H of candidates
+//            and newly found nodes are written back, ascending, behind (-1, -inf)
+//            pads (:138-162);
+//   stage 3  the same search, seeded with the stage-2 result, on the FULL graph
+//            with full-dimension distances, up to 2 * ef expansions, top-k out.
+//
+// The candidates are consumed where the traversal left them, in HBM; nothing of
+// the handoff crosses PCIe.  One CTA of four warps per query, persistent: CTA i
+// owns slot i of the visited-set pool (visited.cu) and walks the batch with
+// stride gridDim.x.  Semantics are upstream's, operation for operation:
+//   * the result heap (H entries) and the open heap (2H entries) are upstream's
+//     array heaps with upstream's routines (extension/inc/heapq.cuh:13-87) --
+//     heap_replace evicts the leaf reached by walking larger children, not the
+//     maximum, so the layout is part of the result; they live in shared memory,
+//     stored 1-based as {key, id} pairs so that both children of a node come in
+//     one 16-byte load, and are driven by one thread;
+//   * H follows upstream's CPU dispatch (traverse_cpu.cpp:228-254);
+//   * exact visited marks (extension/inc/bitmask.hpp:12-45) shared by the two
+//     stages of a query, as upstream shares one marker between them;
+//   * neighbours are taken in row order, a row ends at its first negative id.
+// Distances: one warp per vector row, lane t owns floats [128m + 4t, +4),
+// acc += fma(dx,dx,dy*dy); acc += fma(dz,dz,dw*dw) in ascending m, butterfly
+// 16..1.  Upstream's AVX2 order (eight running sums, built with -ffast-math)
+// differs from this in the last bits, so results agree with upstream's within a
+// relative 1e-5 and with the CPU oracle, which restates this order, bit for bit.
+#include "pa_common.cuh"
+
+namespace pa {
+
+constexpr int kRefThreads = 128;
+constexpr int kRefWarps = kRefThreads / 32;
+#ifndef PA_REFINE_MIN_CTAS
+#define PA_REFINE_MIN_CTAS 7
+#endif
+constexpr int kMaxDegree = 64;
+constexpr int kDupTag = -3;      // a slot whose id repeats an earlier slot of the row: skipped
+constexpr unsigned kAll = 0xffffffffu;
+
+struct RefGraph {
+    const int32_t *nbr;     // neighbour ids
+    const int32_t *row_of;  // node -> row, or nullptr when the row is the node id
+    int64_t row_stride;     // ints between rows
+    int elem_stride;        // ints between the ids of a row
+    int degree;             // slots per row
+};
+
+struct RefineArgs {
+    const int64_t *cand_I;  // [batch, n_cand]
+    const float *cand_D;
+    const float *query;     // [batch, ldq] full rotated queries
+    int64_t ldq;
+    const float *storage;   // [n_nodes, d] full vectors
+    int64_t n_nodes;
+    int d, d_p;
+    RefGraph sub, full;
+    int n_cand, ef, H, k, stages, batch;
+    int64_t *out_I;         // stages 2: [batch, n_cand]; stages 3: [batch, k]
+    float *out_D;
+    uint8_t *marks;         // visited pool: slot s at marks + s * slot_stride
+    int32_t *epoch;         // [slots] last marker used by the slot
+    int64_t slot_stride;
+    int slot_begin;
+    int32_t *stats;         // nullptr or [batch, 4]
+};
+
+// ---- upstream's heaps, 1-based {key, id} pairs, one thread -------------------
+struct __align__(8) HeapEntry {
+    float k;
+    int32_t v;
+};
+
+// h[1 .. n] is the heap (upstream index c lives at c + 1); h[n + 1] exists and is
+// never meaningful: the pair load of the last parent may touch it.
+__device__ __forceinline__ void pair_at(const HeapEntry *h, int child, HeapEntry &l, HeapEntry &r) {
+    const int4 p = *reinterpret_cast<const int4 *>(h + child);  // child is even: 16-byte aligned
+    l.k = __int_as_float(p.x); l.v = p.y;
+    r.k = __int_as_float(p.z); r.v = p.w;
+}
+
+// heapq.cuh:13-29: the root sinks while a child is strictly smaller.
+__device__ __forceinline__ void heap_sink(HeapEntry *h, int n, HeapEntry me) {
+    int cur = 1;
+    for (int child = 2; child <= n; child = 2 * cur) {
+        HeapEntry l, r;
+        pair_at(h, child, l, r);
+        const bool right = (child + 1 <= n) && (r.k < l.k);
+        const HeapEntry c = right ? r : l;
+        if (me.k <= c.k) break;
+        h[cur] = c;
+        cur = child + (right ? 1 : 0);
+    }
+    h[cur] = me;
+}
+
+// heapq.cuh:38-45
+__device__ __forceinline__ HeapEntry heap_pop(HeapEntry *h, int n) {
+    const HeapEntry out = h[1];
+    heap_sink(h, n, HeapEntry{CUDART_INF_F, -1});
+    return out;
+}
+
+// heapq.cuh:79-87
+__device__ __forceinline__ void heap_pushpop(HeapEntry *h, int n, float k, int32_t v) {
+    if (k <= h[1].k) return;
+    heap_sink(h, n, HeapEntry{k, v});
+}
+
+// heapq.cuh:47-77
+__device__ __forceinline__ void heap_replace(HeapEntry *h, int n, float k, int32_t v) {
+    int cur = 1;
+    float cur_k = h[1].k;
+    for (int child = 2; child <= n; child = 2 * cur) {
+        HeapEntry l, r;
+        pair_at(h, child, l, r);
+        const bool right = (child + 1 <= n) && (r.k > l.k);
+        cur = child + (right ? 1 : 0);
+        cur_k = right ? r.k : l.k;
+    }
+    if (k >= cur_k) return;
+    while (cur > 1) {
+        const HeapEntry parent = h[cur >> 1];
+        if (parent.k <= k) break;
+        h[cur] = parent;
+        cur >>= 1;
+    }
+    h[cur] = HeapEntry{k, v};
+}
+
+// ---- distances: one warp per row, two rows in flight ----------------------------
+__device__ __forceinline__ float ref_stripe(float acc, float4 c, float4 p) {
+    const float dx = __fsub_rn(c.x, p.x), dy = __fsub_rn(c.y, p.y);
+    const float dz = __fsub_rn(c.z, p.z), dw = __fsub_rn(c.w, p.w);
+    acc = __fadd_rn(acc, __fmaf_rn(dx, dx, __fmul_rn(dy, dy)));
+    return __fadd_rn(acc, __fmaf_rn(dz, dz, __fmul_rn(dw, dw)));
+}
+
+__device__ __forceinline__ float butterfly(float acc) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(kAll, acc, off));
+    return acc;
+}
+
+// Squared distances of the query to rows r0 and r1 over dims [from, d); every lane
+// returns both sums.  Three stripes of each row are loaded before any arithmetic.
+__device__ __forceinline__ void two_rows(const float *__restrict__ r0, const float *__restrict__ r1,
+                                         const float *q_s, int d, int from, int lane, float &o0,
+                                         float &o1) {
+    float a0 = 0.0f, a1 = 0.0f;
+    for (int o = from + 4 * lane; o < d; o += 384) {
+        float4 x0[3], x1[3];
+#pragma unroll
+        for (int m = 0; m < 3; ++m) {
+            const bool in = o + 128 * m < d;
+            x0[m] = in ? __ldg(reinterpret_cast<const float4 *>(r0 + o + 128 * m))
+                       : make_float4(0, 0, 0, 0);
+            x1[m] = in ? __ldg(reinterpret_cast<const float4 *>(r1 + o + 128 * m))
+                       : make_float4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int m = 0; m < 3; ++m) {
+            if (o + 128 * m < d) {
+                const float4 qa = *reinterpret_cast<const float4 *>(q_s + o + 128 * m);
+                a0 = ref_stripe(a0, qa, x0[m]);
+                a1 = ref_stripe(a1, qa, x1[m]);
+            }
+        }
+    }
+    o0 = butterfly(a0);
+    o1 = butterfly(a1);
+}
+
+struct RefShared {
+    float *q;          // [d]
+    HeapEntry *open;   // [2H + 2]
+    HeapEntry *buf;    // [H + 2]
+    int32_t *c_id;     // [n_cand] seeds of the running stage, then its output
+    float *c_d;
+    int32_t *nb_id;    // [kMaxDegree] unvisited neighbours of the expanded node
+    float *nb_d;
+};
+
+// One call of upstream's traverse_cpu_kernel: seeds in c_id / c_d (n_seed of
+// them), the result (k_out entries, ascending behind (-1, -inf) pads) back into
+// c_id / c_d.  `from` < d: the seeds' distances are first completed over dims
+// [from, d).  Returns expansions and evaluations through n_expand / n_eval
+// (thread 0).
+__device__ __forceinline__ void search_stage(const RefineArgs &A, const RefShared &S,
+                                             const RefGraph &G, uint8_t *vis, uint8_t marker,
+                                             int n_seed, int from, int max_iter, int k_out,
+                                             int *ctl, int &n_expand, int &n_eval) {
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+    const int d = A.d, H = A.H;
+    // distances completed over the trailing dims (:41-62), in place
+    if (from < d) {
+        for (int i = w; i < n_seed; i += 2 * kRefWarps) {
+            const int i1 = i + kRefWarps;
+            const int id0 = S.c_id[i], id1 = i1 < n_seed ? S.c_id[i1] : -1;
+            if (id0 < 0 && id1 < 0) continue;  // warp-uniform
+            float r0, r1;
+            two_rows(A.storage + static_cast<int64_t>(max(id0, 0)) * d,
+                     A.storage + static_cast<int64_t>(max(id1, 0)) * d, S.q, d, from, lane, r0, r1);
+            if (lane == 0) {
+                if (id0 >= 0) S.c_d[i] = __fadd_rn(S.c_d[i], r0);
+                if (id1 >= 0) S.c_d[i1] = __fadd_rn(S.c_d[i1], r1);
+            }
+        }
+    }
+    // :65-68
+    for (int i = tid; i < H + 2; i += kRefThreads) S.buf[i] = HeapEntry{-CUDART_INF_F, -1};
+    for (int i = tid; i < 2 * H + 2; i += kRefThreads) S.open[i] = HeapEntry{CUDART_INF_F, -1};
+    // :69-79, the marks (their order does not matter; the heap inserts below keep it)
+    for (int i = tid; i < n_seed; i += kRefThreads) {
+        const int id = S.c_id[i];
+        if (id >= 0) vis[id] = marker;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        for (int i = 0; i < n_seed; ++i) {
+            const int id = S.c_id[i];
+            if (id >= 0) heap_replace(S.open, 2 * H, S.c_d[i], id);
+        }
+    }
+    // :82-136
+    for (int step = 0; step < max_iter; ++step) {
+        if (tid == 0) {
+            const HeapEntry u = heap_pop(S.open, 2 * H);
+            const bool stop = u.v < 0 || u.k >= -S.buf[1].k;
+            ctl[0] = stop ? -1 : u.v;
+        }
+        __syncthreads();
+        const int u = ctl[0];
+        if (u < 0) break;
+        if (w == 0) {
+            // the row of u in order, up to its first negative id; unvisited ids are
+            // marked and compacted in row order (:105-121)
+            const int64_t row = G.row_of != nullptr ? __ldg(G.row_of + u) : u;
+            int count = 0;
+            bool ended = row < 0;
+            for (int c = 0; c < G.degree; c += 32) {
+                const int slot = c + lane;
+                int v = -1;
+                if (!ended && slot < G.degree)
+                    v = __ldg(G.nbr + row * G.row_stride + static_cast<int64_t>(slot) * G.elem_stride);
+                const unsigned end_mask = __ballot_sync(kAll, v < 0 && v != kDupTag);
+                const int first_end = end_mask ? __ffs(end_mask) - 1 : 32;
+                const bool live = lane < first_end && v >= 0;
+                bool fresh = false;
+                if (live) {
+                    fresh = vis[v] != marker;
+                    if (fresh) vis[v] = marker;
+                }
+                const unsigned m = __ballot_sync(kAll, fresh);
+                if (fresh) S.nb_id[count + __popc(m & ((1u << lane) - 1u))] = v;
+                count += __popc(m);
+                ended = ended || end_mask != 0;
+            }
+            if (lane == 0) ctl[1] = count;
+        }
+        __syncthreads();
+        const int n_new = ctl[1];
+        // full-dimension distances of the unvisited neighbours (:123-135)
+        for (int j = w; j < n_new; j += 2 * kRefWarps) {
+            const int j1 = j + kRefWarps;
+            const int v0 = S.nb_id[j], v1 = j1 < n_new ? S.nb_id[j1] : v0;
+            float r0, r1;
+            two_rows(A.storage + static_cast<int64_t>(v0) * d,
+                     A.storage + static_cast<int64_t>(v1) * d, S.q, d, 0, lane, r0, r1);
+            if (lane == 0) {
+                S.nb_d[j] = r0;
+                if (j1 < n_new) S.nb_d[j1] = r1;
+            }
+        }
+        __syncthreads();
+        if (tid == 0) {  // heap_update (:23-39), row order
+            ++n_expand;
+            n_eval += n_new;
+            for (int j = 0; j < n_new; ++j) {
+                const float dist = S.nb_d[j];
+                if (dist >= -S.buf[1].k) continue;
+                heap_pushpop(S.buf, H, -dist, S.nb_id[j]);
+                heap_replace(S.open, 2 * H, dist, S.nb_id[j]);
+            }
+        }
+    }
+    // :139-162: the seeds join the result heap; all but k_out are dropped; what is
+    // left comes out worst first and is stored ascending
+    const int n_real = min(k_out, H);
+    if (tid == 0) {
+        for (int i = 0; i < n_seed; ++i) {
+            const int id = S.c_id[i];
+            if (id >= 0) heap_pushpop(S.buf, H, -S.c_d[i], id);
+        }
+        for (int i = k_out; i < H; ++i) heap_pop(S.buf, H);
+    }
+    __syncthreads();  // every reader of the seeds is done
+    if (tid == 0) {
+        for (int i = 0; i < n_real; ++i) {
+            const HeapEntry e = heap_pop(S.buf, H);
+            S.c_id[k_out - i - 1] = e.v;
+            S.c_d[k_out - i - 1] = -e.k;
+        }
+    }
+    // pops of an exhausted heap give (-1, key +inf): the leading pads
+    for (int i = tid; i < k_out - n_real; i += kRefThreads) {
+        S.c_id[i] = -1;
+        S.c_d[i] = -CUDART_INF_F;
+    }
+    __syncthreads();
+}
+
+__global__ void __launch_bounds__(kRefThreads, PA_REFINE_MIN_CTAS) refine_kernel(RefineArgs A) {
+    extern __shared__ __align__(16) unsigned char ref_smem[];
+    __shared__ int ctl[4];
+    RefShared S;
+    S.q = reinterpret_cast<float *>(ref_smem);
+    S.open = reinterpret_cast<HeapEntry *>(S.q + A.d);
+    S.buf = S.open + 2 * A.H + 2;
+    S.c_id = reinterpret_cast<int32_t *>(S.buf + A.H + 2);
+    S.c_d = reinterpret_cast<float *>(S.c_id + A.n_cand);
+    S.nb_id = reinterpret_cast<int32_t *>(S.c_d + A.n_cand);
+    S.nb_d = reinterpret_cast<float *>(S.nb_id + kMaxDegree);
+    const int tid = threadIdx.x;
+    const int slot = A.slot_begin + blockIdx.x;
+    uint8_t *vis = A.marks + static_cast<int64_t>(slot) * A.slot_stride;
+
+    for (int64_t b = blockIdx.x; b < A.batch; b += gridDim.x) {
+        // next marker of this slot; the array is wiped when the markers run out
+        // (bitmask.hpp:17-36 does the same on wrap-around)
+        if (tid == 0) ctl[2] = A.epoch[slot] + 1;
+        __syncthreads();
+        int marker = ctl[2];
+        if (marker > 254) {
+            uint4 *p = reinterpret_cast<uint4 *>(vis);
+            for (int64_t i = tid; i < A.slot_stride / 16; i += kRefThreads)
+                p[i] = make_uint4(0, 0, 0, 0);
+            marker = 1;
+        }
+        __syncthreads();
+        if (tid == 0) A.epoch[slot] = marker;
+
+        for (int i = tid; i < A.d; i += kRefThreads) S.q[i] = A.query[b * A.ldq + i];
+        for (int i = tid; i < A.n_cand; i += kRefThreads) {
+            const int64_t id = A.cand_I[b * A.n_cand + i];
+            S.c_id[i] = (id < 0 || id >= A.n_nodes) ? -1 : static_cast<int32_t>(id);
+            S.c_d[i] = A.cand_D[b * A.n_cand + i];
+        }
+        __syncthreads();
+        int st[4] = {0, 0, 0, 0};
+        // stage 2 (traverse_cpu.cpp:317-326): sub-graph, REFINE_STEP expansions
+        search_stage(A, S, A.sub, vis, static_cast<uint8_t>(marker), A.n_cand, A.d_p,
+                     min(2, 2 * A.ef), A.n_cand, ctl, st[0], st[1]);
+        int k_out = A.n_cand;
+        if (A.stages >= 3) {  // stage 3 (:327-336): full graph, same marker
+            search_stage(A, S, A.full, vis, static_cast<uint8_t>(marker), A.n_cand, A.d,
+                         min(1024, 2 * A.ef), A.k, ctl, st[2], st[3]);
+            k_out = A.k;
+        }
+        for (int i = tid; i < k_out; i += kRefThreads) {
+            A.out_I[b * k_out + i] = S.c_id[i];
+            A.out_D[b * k_out + i] = S.c_d[i];
+        }
+        if (A.stats != nullptr && tid == 0) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) A.stats[b * 4 + i] = st[i];
+        }
+        __syncthreads();
+    }
+}
+
+// traverse_cpu.cpp:228-254
+static int cpu_heap_size_for(int ef) {
+    static const int sizes[] = {16, 32, 48, 64, 96, 128, 192, 256, 384, 512, 1024, 2048};
+    for (int s : sizes)
+        if (ef <= s) return s;
+    return -1;
+}
+
+static size_t refine_smem_bytes(int d, int H, int n_cand) {
+    return sizeof(float) * d + sizeof(HeapEntry) * (3 * H + 4) + 8 * static_cast<size_t>(n_cand) +
+           8 * kMaxDegree;
+}
+
+int refine_launch(const RefineArgs &A, int n_slots, cudaStream_t stream) {
+    if (A.batch == 0) return PA_OK;
+    const size_t smem = refine_smem_bytes(A.d, A.H, A.n_cand);
+    static size_t configured[64] = {};
+    int dev = 0;
+    PA_CUDA_TRY(cudaGetDevice(&dev));
+    if (smem > 48 * 1024 && dev >= 0 && dev < 64 && configured[dev] < smem) {
+        PA_CUDA_TRY(cudaFuncSetAttribute(refine_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem)));
+        configured[dev] = smem;
+    }
+    const unsigned grid = static_cast<unsigned>(min(static_cast<int64_t>(A.batch),
+                                                    static_cast<int64_t>(n_slots)));
+    refine_kernel<<<grid, kRefThreads, smem, stream>>>(A);
+    count_launch();
+    PA_CUDA_TRY(cudaGetLastError());
+    return PA_OK;
+}
+
+int refine_check(const void *out_I, const void *out_D, const void *cand_I, const void *cand_D,
+                 const float *query, int64_t ldq, const float *storage, const int32_t *packed_nbr,
+                 const int32_t *row_of, int n_neighbors, const int32_t *full_nbr, int full_degree,
+                 int64_t batch, int64_t n_nodes, int d, int d_p, int n_cand, int ef, int k,
+                 int stages) {
+    PA_REQUIRE(batch >= 0 && batch <= 0x7fffffff, "batch out of range");
+    PA_REQUIRE(stages == 2 || stages == 3, "stages must be 2 (sub-graph stage) or 3 (both)");
+    PA_REQUIRE(ef > 0 && cpu_heap_size_for(ef) > 0, "ef_search must be in (0, 2048]");
+    PA_REQUIRE(d > 0 && d % 4 == 0 && d_p > 0 && d_p % 4 == 0 && d_p <= d,
+               "d_model / d_principle must be multiples of 4 with d_principle <= d_model");
+    PA_REQUIRE(ldq >= d && ldq % 4 == 0, "query row stride must be a multiple of 4");
+    PA_REQUIRE(n_cand > 0 && n_cand % 4 == 0, "the candidate row must be a positive multiple of 4");
+    PA_REQUIRE(n_nodes > 0 && n_nodes < 0x7fffffff, "node ids must fit int32");
+    PA_REQUIRE(n_neighbors > 0 && n_neighbors <= kMaxDegree, "n_neighbors must be in (0, 64]");
+    if (stages >= 3) {
+        PA_REQUIRE(k > 0 && k <= n_cand, "k must be in (0, candidates per query]");
+        PA_REQUIRE(full_degree > 0 && full_degree <= kMaxDegree, "full-graph degree must be in (0, 64]");
+    }
+    PA_REQUIRE(refine_smem_bytes(d, cpu_heap_size_for(ef), n_cand) <= 200 * 1024,
+               "d_model, ef_search and the candidate row together exceed the shared memory of a CTA");
+    if (batch == 0) return PA_OK;
+    PA_REQUIRE(out_I && out_D && cand_I && cand_D && query && storage && packed_nbr && row_of,
+               "null pointer");
+    PA_REQUIRE(stages < 3 || full_nbr != nullptr, "stage 3 needs the packed full graph");
+    PA_REQUIRE(aligned16(query) && aligned16(storage), "query / storage must be 16-byte aligned");
+    return PA_OK;
+}
+
+RefineArgs refine_args(int64_t *out_I, float *out_D, const int64_t *cand_I, const float *cand_D,
+                       const float *query, int64_t ldq, const float *storage,
+                       const int32_t *packed_nbr, const int32_t *row_of, int n_neighbors,
+                       const int32_t *full_nbr, int full_degree, int64_t batch, int64_t n_nodes,
+                       int d, int d_p, int n_cand, int ef, int k, int stages, uint8_t *marks,
+                       int32_t *epoch, int64_t slot_stride, int slot_begin, int32_t *stats) {
+    RefineArgs A;
+    A.cand_I = cand_I; A.cand_D = cand_D; A.query = query; A.ldq = ldq; A.storage = storage;
+    A.n_nodes = n_nodes; A.d = d; A.d_p = d_p;
+    A.sub = RefGraph{packed_nbr, row_of, 4 * static_cast<int64_t>(n_neighbors), 4, n_neighbors};
+    A.full = RefGraph{full_nbr, nullptr, full_degree, 1, full_degree};
+    A.n_cand = n_cand; A.ef = ef; A.H = cpu_heap_size_for(ef); A.k = k; A.stages = stages;
+    A.batch = static_cast<int>(batch);
+    A.out_I = out_I; A.out_D = out_D; A.marks = marks; A.epoch = epoch;
+    A.slot_stride = slot_stride; A.slot_begin = slot_begin; A.stats = stats;
+    return A;
+}
+
+// ---- full graph, packed: int32 [n_nodes, degree], -1 padded ----------------------
+// One thread per node.  A row stops at its first negative id (as the search
+// does); an id that repeats an earlier id of the row is dropped (the search would
+// find it visited), so rows hold distinct ids.
+__global__ void pack_full_kernel(int32_t *__restrict__ out, const int64_t *__restrict__ indptr,
+                                 const int64_t *__restrict__ indices, int64_t n_nodes, int degree,
+                                 int *__restrict__ error) {
+    const int64_t u = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    if (u >= n_nodes) return;
+    const int64_t lo = indptr[u], hi = indptr[u + 1];
+    int32_t *row = out + u * degree;
+    int n = 0;
+    for (int64_t i = lo; i < hi; ++i) {
+        const int64_t v = indices[i];
+        if (v < 0) break;
+        if (v >= n_nodes) { atomicMax(error, 2); break; }
+        bool dup = false;
+        for (int j = 0; j < n; ++j) dup = dup || row[j] == static_cast<int32_t>(v);
+        if (dup) continue;
+        if (n == degree) { atomicMax(error, 1); break; }
+        row[n++] = static_cast<int32_t>(v);
+    }
+    for (; n < degree; ++n) row[n] = -1;
+}
+
+}  // namespace pa
+
+extern "C" int pa_cpu_heap_size_for(int ef_search) { return pa::cpu_heap_size_for(ef_search); }
+
+extern "C" int pa_pack_fullgraph(int32_t *full_nbr, const int64_t *indptr, const int64_t *indices,
+                                 int64_t n_nodes, int degree, void *stream_) {
+    using namespace pa;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    PA_REQUIRE(n_nodes >= 0 && n_nodes < 0x7fffffff, "node ids must fit int32");
+    PA_REQUIRE(degree > 0 && degree <= kMaxDegree, "degree must be in (0, 64]");
+    if (n_nodes == 0) return PA_OK;
+    PA_REQUIRE(full_nbr && indptr && indices, "null pointer");
+    struct ErrorWord {
+        int *p = nullptr;
+        cudaStream_t s;
+        ~ErrorWord() { if (p != nullptr) cudaFreeAsync(p, s); }
+    } word;
+    word.s = stream;
+    PA_CUDA_TRY(cudaMallocAsync(&word.p, sizeof(int), stream));
+    PA_CUDA_TRY(cudaMemsetAsync(word.p, 0, sizeof(int), stream));
+    pack_full_kernel<<<static_cast<unsigned>((n_nodes + 127) / 128), 128, 0, stream>>>(
+        full_nbr, indptr, indices, n_nodes, degree, word.p);
+    count_launch();
+    PA_CUDA_TRY(cudaGetLastError());
+    int host_error = 0;
+    PA_CUDA_TRY(cudaMemcpyAsync(&host_error, word.p, sizeof(int), cudaMemcpyDeviceToHost, stream));
+    PA_CUDA_TRY(cudaStreamSynchronize(stream));
+    if (host_error == 1)
+        return fail(PA_ERR_UNPACKABLE, "a row holds more than `degree` distinct neighbours");
+    if (host_error == 2) return fail(PA_ERR_UNPACKABLE, "a neighbour id is out of range");
+    return PA_OK;
+}

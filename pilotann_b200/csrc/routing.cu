@@ -30,7 +30,8 @@ route_kernel(int64_t *__restrict__ router, float *__restrict__ leaf_D,
              int64_t *__restrict__ leaf_I, const float *__restrict__ query,
              const float *__restrict__ route_vectors, const int64_t *__restrict__ entry_nodes,
              const float *__restrict__ entry_vectors, int d, int64_t ldq, int n_routers,
-             int n_leaves, const float *__restrict__ dots, const float *__restrict__ rnorm2) {
+             int n_leaves, const float *__restrict__ dots, const float *__restrict__ rnorm2,
+             const int *__restrict__ gemm_status) {
     extern __shared__ __align__(16) float q_s[];
     __shared__ double best_d[kRouteThreads];
     __shared__ int best_r[kRouteThreads];
@@ -43,6 +44,8 @@ route_kernel(int64_t *__restrict__ router, float *__restrict__ leaf_D,
     // margin >> the error of a score (a few 1e-6 * |q||r|), so the exact winner and
     // everything tied with it are always on the list.
     float cutoff = CUDART_INF_F;
+    // a tensor-core GEMM that gave up on a bounded wait leaves `dots` unwritten
+    if (dots != nullptr && gemm_status != nullptr && *gemm_status != 0) dots = nullptr;
     if (dots != nullptr) {
         __shared__ float red_a[kRouteThreads], red_b[kRouteThreads], red_c[kRouteThreads];
         float best = CUDART_INF_F, rmax = 0.0f, qn = 0.0f;
@@ -65,48 +68,60 @@ route_kernel(int64_t *__restrict__ router, float *__restrict__ leaf_D,
         cutoff = red_a[0] + 1e-4f * (red_b[0] + red_c[0]);
     }
 
-    // nearest router (route_vectors == nullptr: a single implicit router)
-    double mine = CUDART_INF;
-    int mine_r = 0x7fffffff;
-    if (route_vectors != nullptr) {
-        for (int r = tid; r < n_routers; r += kRouteThreads) {
-            if (dots != nullptr && !(rnorm2[r] - 2.0f * dots[b * n_routers + r] <= cutoff))
-                continue;  // not on the shortlist
-            const float *p = route_vectors + static_cast<int64_t>(r) * d;
-            double acc = 0.0;
-            for (int k = 0; k < d; k += 4) {
-                float4 pv = __ldg(reinterpret_cast<const float4 *>(p + k));
-                float4 qv = *reinterpret_cast<const float4 *>(q_s + k);
-                double d0 = __dsub_rn(double(qv.x), double(pv.x));
-                double d1 = __dsub_rn(double(qv.y), double(pv.y));
-                double d2 = __dsub_rn(double(qv.z), double(pv.z));
-                double d3 = __dsub_rn(double(qv.w), double(pv.w));
-                acc = __dadd_rn(acc, __dmul_rn(d0, d0));
-                acc = __dadd_rn(acc, __dmul_rn(d1, d1));
-                acc = __dadd_rn(acc, __dmul_rn(d2, d2));
-                acc = __dadd_rn(acc, __dmul_rn(d3, d3));
+    // nearest router (route_vectors == nullptr: a single implicit router).  Pass 0
+    // measures the shortlist (every router without tensor-core scores); pass 1
+    // runs only when pass 0 chose nothing -- the scores were unusable (NaN / Inf
+    // in the query, or a GEMM that gave up) -- and measures every router.
+    int r = 0;
+    for (int pass = 0; pass < 2; ++pass) {
+        const bool listed = pass == 0 && dots != nullptr;
+        double mine = CUDART_INF;
+        int mine_r = 0x7fffffff;
+        if (route_vectors != nullptr) {
+            for (int rr = tid; rr < n_routers; rr += kRouteThreads) {
+                if (listed && !(rnorm2[rr] - 2.0f * dots[b * n_routers + rr] <= cutoff))
+                    continue;  // not on the shortlist
+                const float *p = route_vectors + static_cast<int64_t>(rr) * d;
+                double acc = 0.0;
+                for (int k = 0; k < d; k += 4) {
+                    float4 pv = __ldg(reinterpret_cast<const float4 *>(p + k));
+                    float4 qv = *reinterpret_cast<const float4 *>(q_s + k);
+                    double d0 = __dsub_rn(double(qv.x), double(pv.x));
+                    double d1 = __dsub_rn(double(qv.y), double(pv.y));
+                    double d2 = __dsub_rn(double(qv.z), double(pv.z));
+                    double d3 = __dsub_rn(double(qv.w), double(pv.w));
+                    acc = __dadd_rn(acc, __dmul_rn(d0, d0));
+                    acc = __dadd_rn(acc, __dmul_rn(d1, d1));
+                    acc = __dadd_rn(acc, __dmul_rn(d2, d2));
+                    acc = __dadd_rn(acc, __dmul_rn(d3, d3));
+                }
+                if (acc < mine) { mine = acc; mine_r = rr; }  // ascending rr: first minimum
             }
-            if (acc < mine) { mine = acc; mine_r = r; }  // ascending r: first minimum
+        } else if (tid == 0) {
+            mine = 0.0;
+            mine_r = 0;
         }
-    } else if (tid == 0) {
-        mine = 0.0;
-        mine_r = 0;
-    }
-    best_d[tid] = mine;
-    best_r[tid] = mine_r;
-    __syncthreads();
-    for (int off = kRouteThreads / 2; off > 0; off >>= 1) {
-        if (tid < off) {
-            double od = best_d[tid + off];
-            int orr = best_r[tid + off];
-            if (od < best_d[tid] || (od == best_d[tid] && orr < best_r[tid])) {
-                best_d[tid] = od;
-                best_r[tid] = orr;
-            }
-        }
+        __syncthreads();  // the previous pass has read best_r[0]
+        best_d[tid] = mine;
+        best_r[tid] = mine_r;
         __syncthreads();
+        for (int off = kRouteThreads / 2; off > 0; off >>= 1) {
+            if (tid < off) {
+                double od = best_d[tid + off];
+                int orr = best_r[tid + off];
+                if (od < best_d[tid] || (od == best_d[tid] && orr < best_r[tid])) {
+                    best_d[tid] = od;
+                    best_r[tid] = orr;
+                }
+            }
+            __syncthreads();
+        }
+        r = best_r[0];
+        if (static_cast<unsigned>(r) < static_cast<unsigned>(n_routers) || !listed) break;
     }
-    const int r = best_r[0];
+    // No distance compared below +inf (a NaN or Inf query): upstream's argmin still
+    // returns an index in range; router 0 here.  r indexes device memory below.
+    if (static_cast<unsigned>(r) >= static_cast<unsigned>(n_routers)) r = 0;
     if (tid == 0 && router != nullptr) router[b] = r;
 
     // leaves of the chosen router
@@ -171,7 +186,8 @@ int route_launch(int64_t *router, float *leaf_D, int64_t *leaf_I, const float *q
     }
     route_kernel<<<static_cast<unsigned>(batch), kRouteThreads, sizeof(float) * d, stream>>>(
         router, leaf_D, leaf_I, query, route_vectors, entry_nodes, entry_vectors, d, ldq,
-        n_routers, n_leaves, tensor ? dots_ws : nullptr, tensor ? rnorm2 : nullptr);
+        n_routers, n_leaves, tensor ? dots_ws : nullptr, tensor ? rnorm2 : nullptr,
+        tensor ? gemm_status_address() : nullptr);
     count_launch();
     PA_CUDA_TRY(cudaGetLastError());
     return PA_OK;

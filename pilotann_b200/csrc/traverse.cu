@@ -560,10 +560,14 @@ traverse_kernel(Layout L, int64_t *__restrict__ out_I, float *__restrict__ out_D
                     if constexpr (Layout::kPacked) {
                         usable = top_v.y >= 0;
                     } else {
-                        const int64_t at = (pending && !stop) ? top_v.x : 0;
+                        // ids come from the caller's entries and graph: one outside
+                        // [0, n_nodes) reads row 0's bounds and is treated as a node
+                        // without an adjacency row (the packed path drops it at entry)
+                        const bool in_range = top_v.x >= 0 && top_v.x < L.n_nodes;
+                        const int64_t at = (pending && !stop && in_range) ? top_v.x : 0;
                         lo = __ldg(L.indptr + at);
                         hi = __ldg(L.indptr + min(at + 1, L.n_nodes));  // indptr has n_nodes + 1 entries
-                        usable = lo != hi;
+                        usable = in_range && lo != hi;
                     }
                     const bool settle = pending && (stop || usable);
                     // The root is known; removing it from the heap (the sink) can wait
@@ -589,9 +593,12 @@ traverse_kernel(Layout L, int64_t *__restrict__ out_I, float *__restrict__ out_D
                 pop_s[beam].node = u_node; pop_s[beam].row = u_row;
                 pop_s[beam].lo = u_lo; pop_s[beam].len = u_len;
                 pop_s[beam].fetch = fetch;
-                again_s[(outer + 1) & 1] = 0;
             }
             __syncthreads();
+            // The other slot is cleared only now: its last readers (the previous
+            // pass, after that pass's second barrier) are all behind the barrier
+            // above, and its next writers come after this pass's second barrier.
+            if (w == 0) again_s[(outer + 1) & 1] = 0;
             const bool fetch_w = pop_s[w].fetch;  // warp w serves beam w
             const int32_t node_b = pop_s[w].node;
             if constexpr (Layout::kPacked) {
@@ -973,13 +980,12 @@ static int check_common(const void *out_I, const void *out_D, const float *stora
     return PA_OK;
 }
 
-int traverse_packed_launch(int64_t *output_I, float *output_D, const int32_t *packed_nbr,
-                           const int32_t *row_of, const float *storage, const float *query,
-                           int64_t ldq, const int64_t *initial_I, const float *initial_D,
-                           int64_t batch, int64_t n_nodes, int64_t n_storage, int d_model,
-                           int n_neighbors, int n_initials, int ef_search, int32_t *stats,
-                           cudaStream_t stream) {
-    (void)n_storage;
+// Every argument check of the packed-layout search, without launching anything.
+int traverse_packed_check(const int64_t *output_I, const float *output_D,
+                          const int32_t *packed_nbr, const int32_t *row_of, const float *storage,
+                          const float *query, int64_t ldq, const int64_t *initial_I,
+                          const float *initial_D, int64_t batch, int64_t n_nodes, int d_model,
+                          int n_neighbors, int n_initials, int ef_search) {
     int rc = check_common(output_I, output_D, storage, query, initial_I, initial_D, batch, n_nodes,
                           d_model, n_neighbors, n_initials, ef_search);
     if (rc != PA_OK || batch == 0) return rc;
@@ -987,6 +993,20 @@ int traverse_packed_launch(int64_t *output_I, float *output_D, const int32_t *pa
     PA_REQUIRE((reinterpret_cast<uintptr_t>(packed_nbr) & 15u) == 0,
                "packed_nbr must be 16-byte aligned");
     PA_REQUIRE(ldq >= d_model && ldq % 4 == 0, "query row stride must be a multiple of 4");
+    return PA_OK;
+}
+
+int traverse_packed_launch(int64_t *output_I, float *output_D, const int32_t *packed_nbr,
+                           const int32_t *row_of, const float *storage, const float *query,
+                           int64_t ldq, const int64_t *initial_I, const float *initial_D,
+                           int64_t batch, int64_t n_nodes, int64_t n_storage, int d_model,
+                           int n_neighbors, int n_initials, int ef_search, int32_t *stats,
+                           cudaStream_t stream) {
+    (void)n_storage;
+    int rc = traverse_packed_check(output_I, output_D, packed_nbr, row_of, storage, query, ldq,
+                                   initial_I, initial_D, batch, n_nodes, d_model, n_neighbors,
+                                   n_initials, ef_search);
+    if (rc != PA_OK || batch == 0) return rc;
     PackedLayout L{reinterpret_cast<const int4 *>(packed_nbr), row_of, storage, n_nodes};
     return launch(L, output_I, output_D, query, ldq, initial_I, initial_D, batch, d_model,
                   n_neighbors, n_initials, ef_search, stats, stream);

@@ -12,6 +12,8 @@ current torch CUDA stream of the tensors' device, like upstream
 """
 from __future__ import annotations
 
+import threading
+
 import torch
 
 from . import _C
@@ -64,10 +66,13 @@ def _traverse_checks(output_I, output_D, storage, query, initial_I, initial_D, n
 # on the second call, and searched in the packed layout from then on: identical
 # results, ~20 % less time per call.  An entry is used only while the three
 # tensor objects are alive and unmodified (torch's version counters); a graph
-# that cannot be packed keeps the CSR path.  PILOTANN_B200_PACK_CACHE=0 turns
-# this off.
+# that cannot be packed keeps the CSR path (the reason is kept in the entry).
+# Packing allocates device memory and synchronises the stream once; it is never
+# done while the current stream is being captured into a CUDA graph (the call
+# then stays on the CSR path).  PILOTANN_B200_PACK_CACHE=0 turns this off.
 _PACK_CACHE_SLOTS = 2
 _pack_cache: dict = {}
+_pack_lock = threading.Lock()
 
 
 def _packed_for(indptr, indices, mapping, n_storage: int, n_neighbors: int):
@@ -75,26 +80,32 @@ def _packed_for(indptr, indices, mapping, n_storage: int, n_neighbors: int):
     import weakref
     if os.environ.get("PILOTANN_B200_PACK_CACHE", "1") == "0":
         return None
+    if torch.cuda.is_current_stream_capturing():
+        capturing = True                 # no allocation, no synchronise under capture
+    else:
+        capturing = False
     key = (indptr.data_ptr(), indices.data_ptr(), mapping.data_ptr(), indptr.numel(),
            indices.numel(), n_storage, n_neighbors, indptr.device.index)
     stamp = (indptr._version, indices._version, mapping._version)
-    for dead in [k for k, e in _pack_cache.items() if any(r() is None for r in e["refs"])]:
-        del _pack_cache[dead]            # the caller's tensors are gone: free their packed form
-    entry = _pack_cache.get(key)
-    alive = entry is not None and all(r() is x for r, x in
-                                      zip(entry["refs"], (indptr, indices, mapping)))
-    if not alive or entry["stamp"] != stamp:
-        while len(_pack_cache) >= _PACK_CACHE_SLOTS and key not in _pack_cache:
-            _pack_cache.pop(next(iter(_pack_cache)))
-        _pack_cache[key] = {"refs": tuple(weakref.ref(x) for x in (indptr, indices, mapping)),
-                            "stamp": stamp, "packed": None, "usable": True}
-        return None                      # first sight of these tensors: search them as they are
-    if entry["packed"] is None and entry["usable"]:
-        try:
-            entry["packed"] = pack_graph(indptr, indices, mapping, n_storage, n_neighbors)
-        except RuntimeError:
-            entry["usable"] = False      # e.g. a node with neighbours but no vector row
-    return entry["packed"]
+    with _pack_lock:
+        for dead in [k for k, e in _pack_cache.items() if any(r() is None for r in e["refs"])]:
+            del _pack_cache[dead]        # the caller's tensors are gone: free their packed form
+        entry = _pack_cache.get(key)
+        alive = entry is not None and all(r() is x for r, x in
+                                          zip(entry["refs"], (indptr, indices, mapping)))
+        if not alive or entry["stamp"] != stamp:
+            while len(_pack_cache) >= _PACK_CACHE_SLOTS and key not in _pack_cache:
+                _pack_cache.pop(next(iter(_pack_cache)))
+            _pack_cache[key] = {"refs": tuple(weakref.ref(x) for x in (indptr, indices, mapping)),
+                                "stamp": stamp, "packed": None, "usable": True, "why": None}
+            return None                  # first sight of these tensors: search them as they are
+        if entry["packed"] is None and entry["usable"] and not capturing:
+            try:
+                entry["packed"] = pack_graph(indptr, indices, mapping, n_storage, n_neighbors)
+            except RuntimeError as exc:
+                entry["usable"] = False  # e.g. a node with neighbours but no vector row
+                entry["why"] = str(exc)
+        return entry["packed"]
 
 
 def traverse_cuda(output_I, output_D, indptr, indices, mapping, storage, query,
@@ -253,8 +264,18 @@ def search_reduced_noalloc(output_I, output_D, packed_nbr, row_of, storage, quer
     if route_vectors is not None:
         _check_cuda("route_vectors", route_vectors, 2, torch.float32)
     batch, d = query.shape
+    n_leaves = entry_nodes.size(-1)
+    _require(packed_nbr.size(0) == storage.size(0), "packed_nbr.size(0) == n_storage")
+    _require(packed_nbr.size(1) == n_neighbors, "packed_nbr.size(1) == n_neighbors")
     _require(packed_nbr.size(2) == 4, "packed_nbr.size(2) == 4")
     _require(storage.size(1) == d, "storage.size(-1) == d_principle")
+    _require(entry_vectors.size(-1) == d, "entry_vectors.size(-1) == d_principle")
+    _require(entry_vectors.size(-2) == n_leaves, "entry_vectors.size(-2) == n_leaves")
+    if route_vectors is not None:
+        n_routers = route_vectors.size(0)
+        _require(route_vectors.size(1) == d, "route_vectors.size(-1) == d_principle")
+        _require(entry_nodes.size(0) == n_routers, "entry_nodes.size(0) == n_routers")
+        _require(entry_vectors.size(0) == n_routers, "entry_vectors.size(0) == n_routers")
     _require(output_I.shape == output_D.shape and output_I.size(0) == batch
              and output_I.size(1) == BEAM_WIDTH, "output shape [batch, 4, ef]")
     with torch.cuda.device(query.device):

@@ -11,7 +11,7 @@ from pilotann_b200 import utils
 @functools.lru_cache(maxsize=32)
 def make_problem(n: int = 4096, d: int = 64, n_nb: int = 32, ratio: float = 1.0,
                  batch: int = 64, n_init: int = 32, seed: int = 0, law: str = "fuzz",
-                 exact_entries: bool = True, build_device: str = "cpu"):
+                 exact_entries: bool = True, build_device: str = "cpu", graph: str = "nsw"):
     """A graph over n vectors of dim d (already 'reduced'), optionally sampled.
     Returns a dict of CPU tensors in the layout ``traverse_cuda`` takes
     (``extension/entry.cpp:32-38``)."""
@@ -20,15 +20,15 @@ def make_problem(n: int = 4096, d: int = 64, n_nb: int = 32, ratio: float = 1.0,
         x = 2.0 * (torch.rand(n, d, generator=g) - 0.5)
         q = 2.0 * (torch.rand(batch, d, generator=g) - 0.5)
     else:
-        w = utils.WORKLOADS[2 if law == "powerlaw" else 1]
+        w = utils.WORKLOADS[{"powerlaw": 2, "powerlaw-ood": 3}.get(law, 1)]
         w = w.scaled(n, batch)
         w = type(w)(**{**w.__dict__, "d_model": d})
         x, q = utils.make_storage(w), utils.make_queries(w)
     dev = torch.device(build_device)
-    indptr, indices = utils.graph_init(x.to(dev), "nsw", n_nb)
+    indptr, indices = utils.graph_init(x.to(dev), graph, n_nb)
     if ratio < 1.0:
         indptr, indices, nodelist, mapping = utils.subgraph_init(
-            indptr, indices, x, "nsw", n_samples=int(ratio * n), n_neighbors=n_nb,
+            indptr, indices, x, graph, n_samples=int(ratio * n), n_neighbors=n_nb,
             generator=g, device=dev)
         storage = x[nodelist].contiguous()
     else:

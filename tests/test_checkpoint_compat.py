@@ -9,14 +9,16 @@ import types
 import pytest
 import torch
 
-REFERENCE = os.environ.get("PILOTANN_REFERENCE", "/root/reference")
+from oracle import build_ref
+
+_root = build_ref.reference_root()        # $PILOTANN_REFERENCE, else ../reference beside the repo
+REFERENCE = str(_root) if _root is not None else ""
 
 
 @pytest.fixture(scope="module")
 def upstream_layers():
-    if not os.path.isdir(os.path.join(REFERENCE, "pilot_ann")):
+    if not REFERENCE or not os.path.isdir(os.path.join(REFERENCE, "pilot_ann")):
         pytest.skip("upstream sources not present")
-    from oracle import build_ref
     ext = build_ref.load()
     if ext is None:
         pytest.skip("oracle/_ref/extension.so not built")

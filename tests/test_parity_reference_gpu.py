@@ -51,18 +51,26 @@ def _recall(top, truth):
     return hit / sum(len(b) for b in truth)
 
 
-@pytest.mark.parametrize("law,d,ratio,ef", [("fuzz", 64, 1.0, 64), ("powerlaw", 128, 0.25, 32),
-                                            ("mixture", 64, 0.25, 32), ("powerlaw", 128, 0.25, 128)])
-def test_traversal_vs_upstream_kernel(ref_ext, law, d, ratio, ef):
-    k = 10
-    p = make_problem(n=20000, d=d, ratio=ratio, batch=512, n_init=64, seed=21, law=law,
-                     build_device="cuda")
+# (law, d, sample ratio, ef, entries per query, k, graph flavour); the last two rows
+# are the reduced-size shapes of the 96-d L2 configuration (shared random entries:
+# 32 of them, heaps of 32) and of the 200-d out-of-distribution one (d_principle 96,
+# half the nodes sampled, 32 leaves per router, top-100, ef 128, NSG-style graph)
+CASES = [("fuzz", 64, 1.0, 64, 64, 10, "nsw"), ("powerlaw", 128, 0.25, 32, 64, 10, "nsw"),
+         ("mixture", 64, 0.25, 32, 64, 10, "nsw"), ("powerlaw", 128, 0.25, 128, 64, 10, "nsw"),
+         ("mixture", 64, 0.25, 32, 32, 10, "nsw"), ("powerlaw-ood", 96, 0.5, 128, 32, 100, "nsg")]
+
+
+@pytest.mark.parametrize("law,d,ratio,ef,n_init,k,graph", CASES)
+def test_traversal_vs_upstream_kernel(ref_ext, law, d, ratio, ef, n_init, k, graph):
+    p = make_problem(n=20000, d=d, ratio=ratio, batch=512, n_init=n_init, seed=21, law=law,
+                     build_device="cuda", graph=graph)
     c = to_cuda(p)
     # Upstream's kernel is racy: its own runs disagree with each other.  Five runs
     # give its run-to-run mismatch rate (mean over the ten pairs); the deterministic
     # kernel must look like one more such run: its mean mismatch against the five
     # stays within 1.5 x that rate plus four standard deviations of a rate estimated
-    # on this many queries (plus 0.01 of slack, and never less than the 0.5 % gate).
+    # on this many queries, and never less than the 0.5 % gate -- which is the whole
+    # gate wherever upstream reproduces itself (rate 0, deviation 0).
     # 1.5 x: upstream's runs share their timing habits and sit closer to each other
     # than to any other legal interleaving (measured: 0.14 against 0.095 on the
     # uniform-random workload, where revisits are most frequent; equal elsewhere).
@@ -75,7 +83,7 @@ def test_traversal_vs_upstream_kernel(ref_ext, law, d, ratio, ef):
 
     pairs = [(i, j) for i in range(5) for j in range(i + 1, 5)]
     jitter = sum(mismatch(tops[i], tops[j]) for i, j in pairs) / len(pairs)
-    sigma = (max(jitter, 0.002) * (1.0 - jitter) / n_q) ** 0.5
+    sigma = (jitter * (1.0 - jitter) / n_q) ** 0.5
     theirs, t_top = runs[0], tops[0]
     truth = p["nodelist"][__import__("pilotann_b200").utils.ground_truth(
         p["query"], p["full"][p["nodelist"]], k)].tolist()
@@ -86,7 +94,7 @@ def test_traversal_vs_upstream_kernel(ref_ext, law, d, ratio, ef):
         miss = sum(mismatch(o_top, tp) for tp in tops) / 5
         print(f"{law} d={d} ef={ef} packed={packed}: mismatch against upstream {miss:.4f} "
               f"(upstream run-to-run {jitter:.4f}, sigma {sigma:.4f})")
-        assert miss <= max(0.005, 1.5 * jitter + 4.0 * sigma + 0.01)
+        assert miss <= max(0.005, 1.5 * jitter + 4.0 * sigma)
         # recall: never worse than upstream beyond +-0.002 (+ upstream's own noise: a
         # query whose top-k differs typically differs in about one of its k ids).  It
         # may be better by up to the mismatch rate: upstream's races insert some nodes
@@ -175,7 +183,7 @@ def test_pipeline_drop_in_vs_upstream_pipeline(ref_ext):
     theirs = [upstream()[0] for _ in range(4)]
     pairs = [(i, j) for i in range(4) for j in range(i + 1, 4)]
     jitter = sum(mismatch(theirs[i], theirs[j]) for i, j in pairs) / len(pairs)
-    sigma = (max(jitter, 0.002) * (1.0 - jitter) / ours_I.size(0)) ** 0.5
+    sigma = (jitter * (1.0 - jitter) / ours_I.size(0)) ** 0.5
     miss = sum(mismatch(ours_I, th) for th in theirs) / 4
     truth = utils.ground_truth(p["query"], p["full"], k)
     r_ours = utils.recall(ours_I, truth)
@@ -183,6 +191,6 @@ def test_pipeline_drop_in_vs_upstream_pipeline(ref_ext):
     print(f"pipeline recall ours {r_ours:.4f} upstream {r_theirs:.4f}, top-{k} mismatch {miss:.4f} "
           f"(upstream run-to-run {jitter:.4f}, sigma {sigma:.4f})")
     assert abs(r_ours - r_theirs) <= 0.005
-    assert miss <= max(0.005, 1.5 * jitter + 4.0 * sigma + 0.01)
+    assert miss <= max(0.005, 1.5 * jitter + 4.0 * sigma)
     exact = torch.cdist(p["query"].unsqueeze(1), p["full"][ours_I]).squeeze(1).square()
     assert torch.allclose(ours_D, exact, atol=1e-3)

@@ -98,3 +98,42 @@ def test_sizes_beyond_the_static_scratch_are_refused():
     with pytest.raises(RuntimeError, match="PA_NOALLOC_MAX_LEAVES"):
         extension.search_reduced_noalloc(oI[:8], oD[:8], nbr, row_of, c["storage"],
                                          c["query"][:8].contiguous(), rv, en, ev, 32)
+
+
+def test_mismatched_shapes_are_refused_on_the_host_and_nothing_is_allocated():
+    """Shapes that would make the kernels read past a table are turned down by
+    the wrapper before anything is enqueued; a good call leaves torch's
+    allocation counter where it was."""
+    from pilotann_b200 import extension
+    p = make_problem(n=6000, d=64, ratio=0.5, batch=64, n_init=32, seed=31)
+    c = to_cuda(p)
+    nbr, row_of = extension.pack_graph(c["indptr"], c["indices"], c["mapping"],
+                                       c["storage"].size(0), 32)
+    rv, en, ev = _tables(p, 4, 64, 7)
+    q = c["query"]
+    oI = torch.empty(64, 4, 16, dtype=torch.int64, device="cuda")
+    oD = torch.empty(64, 4, 16, device="cuda")
+    bad = [
+        dict(ev=ev[:, :, :32].contiguous()),          # leaf vectors of another dimension
+        dict(ev=ev[:3].contiguous()),                 # fewer routers than route_vectors
+        dict(ev=ev[:, :32].contiguous()),             # fewer leaves than entry_nodes
+        dict(rv=rv[:, :32].contiguous()),             # router vectors of another dimension
+        dict(en=en[:2].contiguous()),                 # entry_nodes for fewer routers
+        dict(nbr=nbr[:-1].contiguous()),              # packed rows != storage rows
+        dict(n_nb=64),                                # degree other than the packed one
+    ]
+    launches = extension.launch_count()
+    for change in bad:
+        a = dict(rv=rv, en=en, ev=ev, nbr=nbr, n_nb=32)
+        a.update(change)
+        with pytest.raises(RuntimeError):
+            extension.search_reduced_noalloc(oI, oD, a["nbr"], row_of, c["storage"], q, a["rv"],
+                                             a["en"], a["ev"], a["n_nb"])
+    assert extension.launch_count() == launches           # nothing was enqueued
+    torch.cuda.synchronize()
+    extension.search_reduced_noalloc(oI, oD, nbr, row_of, c["storage"], q, rv, en, ev, 32)  # set-up
+    torch.cuda.synchronize()
+    before = torch.cuda.memory_allocated()
+    extension.search_reduced_noalloc(oI, oD, nbr, row_of, c["storage"], q, rv, en, ev, 32)
+    torch.cuda.synchronize()
+    assert torch.cuda.memory_allocated() == before
