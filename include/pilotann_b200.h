@@ -138,6 +138,53 @@ int pa_device_status(int reset);
  * router exactly.  No upstream counterpart. */
 int pa_selftest_bounded_wait(void *stream);
 
+/* ---- visited-set pool -------------------------------------------------------
+ * Device counterpart of upstream's `Bitmask` / `BitmaskPool`
+ * (extension/inc/bitmask.hpp:12-45, 51-76; used at traverse_cpu.cpp:196-200 and
+ * 297-312): per worker an array of epoch markers over all nodes, so that the
+ * visited state of a query never needs clearing.  A worker here is a resident
+ * CTA of the refinement kernel; slot i belongs to CTA i of a launch, one byte per
+ * node, markers 1..254, wiped on wrap-around.  Allocates
+ * pa_visited_pool_bytes(n_nodes, n_slots) bytes of device memory once.  Launches
+ * that may overlap on the GPU must not share a pool (the stage object gives each
+ * of its streams its own slots). */
+typedef struct pa_visited_pool pa_visited_pool;
+int64_t pa_visited_pool_bytes(int64_t n_nodes, int n_slots);
+int pa_visited_pool_create(pa_visited_pool **out, int64_t n_nodes, int n_slots);
+void pa_visited_pool_destroy(pa_visited_pool *pool);
+int pa_visited_pool_slots(const pa_visited_pool *pool);
+
+/* ---- refinement on the GPU ---------------------------------------------------
+ * Replaces the CPU consumer of the handoff, `traverse_refine`
+ * (extension/traverse_cpu.cpp:261-369, declared in extension/entry.cpp:39-46),
+ * i.e. two calls of `traverse_cpu_kernel` (traverse_cpu.cpp:12-163) per query:
+ * stage 2 on the sampled sub-graph (distances completed over dims d_principle ..
+ * d_model, REFINE_STEP = 2 expansions, result written back over the handoff row)
+ * and stage 3 on the full graph (top-k).  Heap capacity H follows upstream's CPU
+ * dispatch (traverse_cpu.cpp:228-254): pa_cpu_heap_size_for(ef_search).
+ *   cand_I / cand_D [batch, n_cand]: the handoff as pa_traverse_* wrote it
+ *     (n_cand = 4 * ef_search), read only
+ *   query [batch, d_model]: the full rotated queries
+ *   storage_full [n_nodes, d_model] f32
+ *   packed_nbr / row_of / n_neighbors: the packed sub-graph (pa_pack_graph)
+ *   full_nbr [n_nodes, full_degree] int32: pa_pack_fullgraph (stages == 3 only)
+ *   stages 2: out_I / out_D [batch, n_cand] <- the stage-2 row (what upstream leaves
+ *     in the handoff buffer: H best ascending behind (-1, -inf) pads);
+ *   stages 3: out_I [batch, k] int64, out_D [batch, k] f32 <- top-k ascending.
+ *   stats: NULL or int32 [batch, 4] = stage-2 expansions, stage-2 distance
+ *     evaluations, stage-3 expansions, stage-3 evaluations.
+ * Distances are summed in this kernel's own order (see csrc/refine.cu); against
+ * upstream's AVX2 build they agree within 1e-5 relative. */
+int pa_cpu_heap_size_for(int ef_search);
+int pa_pack_fullgraph(int32_t *full_nbr, const int64_t *indptr, const int64_t *indices,
+                      int64_t n_nodes, int degree, void *stream);
+int pa_refine(int64_t *out_I, float *out_D, const int64_t *cand_I, const float *cand_D,
+              const float *query, const float *storage_full, const int32_t *packed_nbr,
+              const int32_t *row_of, int n_neighbors, const int32_t *full_nbr,
+              int full_degree, int64_t batch, int64_t n_nodes, int d_model,
+              int d_principle, int n_cand, int ef_search, int k, int stages,
+              pa_visited_pool *pool, int32_t *stats, void *stream);
+
 /* ---- search stage object -------------------------------------------------
  * Replaces the GPU half of `pipeline` (extension/pipeline_cpu.cpp:32-145): its
  * static stream pool (:67-75), the per-call device and pinned handoff buffers
@@ -182,6 +229,57 @@ int pa_stage_search(pa_stage *stage, const float *host_query, float *host_rotate
 int pa_stage_search_device(pa_stage *stage, const float *dev_query,
                            int64_t *dev_out_I, float *dev_out_D, int64_t batch,
                            int ef_search, int32_t *dev_stats);
+/* ---- refinement inside the stage ---------------------------------------------
+ * With refinement data attached the stage can go on where the handoff used to
+ * leave the GPU: the candidates stay in HBM and pa_refine's kernel consumes them
+ * on the same stream.  What a call returns is chosen by `mode`:
+ *   PA_OUT_HANDOFF  [batch, 4*ef]  the traversal's candidates (pa_stage_search)
+ *   PA_OUT_STAGE2   [batch, 4*ef]  the rows after the sub-graph stage of
+ *                                  `traverse_refine` (traverse_cpu.cpp:317-326):
+ *                                  feed them to upstream `traverse_cpu` for stage 3
+ *   PA_OUT_TOPK     [batch, k]     both stages: the final top-k, ascending
+ * pa_stage_attach_refine allocates, once: the stage's visited pool
+ * (slots_per_stream slots for each stream; 0 = one wave of CTAs) and the device
+ * buffers of the refined rows.  storage_full / full_nbr are borrowed.  full_nbr
+ * may be NULL when only PA_OUT_STAGE2 is wanted. */
+#define PA_OUT_HANDOFF 0
+#define PA_OUT_STAGE2 1
+#define PA_OUT_TOPK 2
+typedef struct pa_refine_index {
+    const float *storage_full;   /* [n_nodes, d_model] rotated full vectors */
+    const int32_t *full_nbr;     /* [n_nodes, full_degree] pa_pack_fullgraph, or NULL */
+    int full_degree;
+} pa_refine_index;
+int pa_stage_attach_refine(pa_stage *stage, const pa_refine_index *refine,
+                           int slots_per_stream);
+/* pa_stage_search / pa_stage_search_device with a choice of output; k is used by
+ * PA_OUT_TOPK only.  dev_refine_stats: NULL or int32 [batch, 4] as pa_refine. */
+int pa_stage_search_ex(pa_stage *stage, const float *host_query, float *host_rotated,
+                       int64_t *host_out_I, float *host_out_D, int64_t batch,
+                       int ef_search, int k, int mode, int64_t chunk);
+int pa_stage_search_device_ex(pa_stage *stage, const float *dev_query,
+                              int64_t *dev_out_I, float *dev_out_D, int64_t batch,
+                              int ef_search, int k, int mode, int32_t *dev_stats,
+                              int32_t *dev_refine_stats);
+
+/* ---- submit / wait ---------------------------------------------------------------
+ * Replaces the software pipeline of upstream `pipeline`
+ * (extension/pipeline_cpu.cpp:99-141: the CPU refines chunk i-2 while the GPU
+ * traverses chunk i-1) without its per-call buffers (:78-96).  The stage has one
+ * slot per stream; a slot takes up to pa_stage_slot_rows() queries.
+ * pa_stage_submit copies the chunk in, enqueues the kernels of `mode` and the
+ * copy back into the slot's own pinned host buffers, and returns; pa_stage_wait
+ * blocks until that chunk is complete and hands out the slot's buffers
+ * (host_out_* rows of the mode's length, host_rotated [n, d_model] when the
+ * submit asked for the rotated queries), valid until the slot's next submit.
+ * The pinned buffers are allocated by the first submit and live as long as the
+ * stage.  One thread drives a stage. */
+int64_t pa_stage_slot_rows(pa_stage *stage);
+int pa_stage_submit(pa_stage *stage, int slot, const float *host_query, int64_t n,
+                    int ef_search, int k, int mode, int want_rotated);
+int pa_stage_wait(pa_stage *stage, int slot, int64_t **host_out_I, float **host_out_D,
+                  float **host_rotated, int64_t *n_rows);
+
 int pa_stage_synchronize(pa_stage *stage);
 /* cudaStream_t of the stage's first stream (for event timing by the caller). */
 void *pa_stage_stream(pa_stage *stage);

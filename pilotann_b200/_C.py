@@ -21,7 +21,9 @@ SYMBOLS = (
     "pa_traverse_packed", "pa_route", "pa_project", "pa_stage_create", "pa_stage_destroy",
     "pa_stage_search", "pa_stage_search_device", "pa_stage_synchronize", "pa_stage_stream",
     "pa_launch_count", "pa_search_reduced_noalloc", "pa_device_status", "pa_route_ws", "pa_route_workspace_floats",
-    "pa_selftest_bounded_wait",
+    "pa_selftest_bounded_wait", "pa_visited_pool_bytes", "pa_visited_pool_create",
+    "pa_visited_pool_destroy", "pa_visited_pool_slots", "pa_cpu_heap_size_for",
+    "pa_pack_fullgraph", "pa_refine",
 )
 
 
@@ -72,6 +74,21 @@ def lib() -> ctypes.CDLL:
     L.pa_stage_stream.argtypes = [P]
     L.pa_stage_stream.restype = P
     L.pa_launch_count.restype = c_int64
+    L.pa_visited_pool_bytes.argtypes = [c_int64, c_int]
+    L.pa_visited_pool_bytes.restype = c_int64
+    L.pa_visited_pool_create.argtypes = [POINTER(P), c_int64, c_int]
+    L.pa_visited_pool_create.restype = c_int
+    L.pa_visited_pool_destroy.argtypes = [P]
+    L.pa_visited_pool_destroy.restype = None
+    L.pa_visited_pool_slots.argtypes = [P]
+    L.pa_visited_pool_slots.restype = c_int
+    L.pa_cpu_heap_size_for.argtypes = [c_int]
+    L.pa_cpu_heap_size_for.restype = c_int
+    L.pa_pack_fullgraph.argtypes = [P, P, P, c_int64, c_int, P]
+    L.pa_pack_fullgraph.restype = c_int
+    L.pa_refine.argtypes = [P, P, P, P, P, P, P, P, c_int, P, c_int, c_int64, c_int64, c_int,
+                            c_int, c_int, c_int, c_int, c_int, P, P, P]
+    L.pa_refine.restype = c_int
     L.pa_selftest_bounded_wait.argtypes = [P]
     L.pa_selftest_bounded_wait.restype = c_int
     L.pa_device_status.argtypes = [c_int]

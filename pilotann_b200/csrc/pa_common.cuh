@@ -51,6 +51,17 @@ const int *gemm_status_address();
 int project_launch(float *out, const float *query, const float *VT, int64_t batch, int d,
                    int d_out, int64_t ld_out, cudaStream_t stream);
 
+void pool_view(const pa_visited_pool *pool, uint8_t **marks, int32_t **epoch, int64_t *slot_stride,
+               int *n_slots, int64_t *n_nodes);
+
+int refine_enqueue(int64_t *out_I, float *out_D, const int64_t *cand_I, const float *cand_D,
+                   const float *query, int64_t ldq, const float *storage_full,
+                   const int32_t *packed_nbr, const int32_t *row_of, int n_neighbors,
+                   const int32_t *full_nbr, int full_degree, int64_t batch, int64_t n_nodes,
+                   int d_model, int d_principle, int n_cand, int ef_search, int k, int stages,
+                   const pa_visited_pool *pool, int slot_begin, int slot_count, int32_t *stats,
+                   cudaStream_t stream);
+
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // ---- constants with search semantics (upstream traverse_cuda.cu:7-15) ----
@@ -64,6 +75,7 @@ constexpr int kFnvSteps = 4;            // FNV_STEP
 constexpr uint32_t kFnvPrime = 0x01000193u;
 constexpr uint32_t kFnvOffset = 0x811c9dc5u;
 constexpr int kEmptyRowTag = -2;       // first pair of a packed row without adjacency
+constexpr int kDupTag = -3;            // a slot whose id repeats an earlier slot of its row
 
 // upstream bloom.cuh:9-16: the whole shifted word is xor-ed in at every step
 __host__ __device__ __forceinline__ uint32_t fnv1a_32(uint32_t x, uint32_t h) {

@@ -35,8 +35,14 @@ __global__ void pack_rows_kernel(int4 *__restrict__ nbr, int32_t *__restrict__ r
             int64_t v = indices[lo + i];
             if (v >= n_nodes) { atomicMax(error, 2); v = -1; }
             if (v >= 0) {
+                // an id that repeats an earlier slot of the row: every search finds it
+                // visited by then (the bloom filter of the traversal, the exact marks
+                // of the refinement), so the slot is tagged and skipped
+                bool dup = false;
+                for (int j = 0; j < i; ++j) dup = dup || indices[lo + j] == v;
                 int64_t r = mapping[v];
-                e = make_int2(static_cast<int32_t>(v), r < 0 ? -1 : static_cast<int32_t>(r));
+                e = dup ? make_int2(kDupTag, -1)
+                        : make_int2(static_cast<int32_t>(v), r < 0 ? -1 : static_cast<int32_t>(r));
             }
         }
         // the bloom probes of the slot: a chunk of 32 slots is what the search

@@ -40,7 +40,6 @@ constexpr int kRefWarps = kRefThreads / 32;
 #define PA_REFINE_MIN_CTAS 7
 #endif
 constexpr int kMaxDegree = 64;
-constexpr int kDupTag = -3;      // a slot whose id repeats an earlier slot of the row: skipped
 constexpr unsigned kAll = 0xffffffffu;
 
 struct RefGraph {
@@ -387,7 +386,7 @@ static size_t refine_smem_bytes(int d, int H, int n_cand) {
            8 * kMaxDegree;
 }
 
-int refine_launch(const RefineArgs &A, int n_slots, cudaStream_t stream) {
+static int refine_launch(const RefineArgs &A, int n_slots, cudaStream_t stream) {
     if (A.batch == 0) return PA_OK;
     const size_t smem = refine_smem_bytes(A.d, A.H, A.n_cand);
     static size_t configured[64] = {};
@@ -406,7 +405,7 @@ int refine_launch(const RefineArgs &A, int n_slots, cudaStream_t stream) {
     return PA_OK;
 }
 
-int refine_check(const void *out_I, const void *out_D, const void *cand_I, const void *cand_D,
+static int refine_check(const void *out_I, const void *out_D, const void *cand_I, const void *cand_D,
                  const float *query, int64_t ldq, const float *storage, const int32_t *packed_nbr,
                  const int32_t *row_of, int n_neighbors, const int32_t *full_nbr, int full_degree,
                  int64_t batch, int64_t n_nodes, int d, int d_p, int n_cand, int ef, int k,
@@ -434,7 +433,7 @@ int refine_check(const void *out_I, const void *out_D, const void *cand_I, const
     return PA_OK;
 }
 
-RefineArgs refine_args(int64_t *out_I, float *out_D, const int64_t *cand_I, const float *cand_D,
+static RefineArgs refine_args(int64_t *out_I, float *out_D, const int64_t *cand_I, const float *cand_D,
                        const float *query, int64_t ldq, const float *storage,
                        const int32_t *packed_nbr, const int32_t *row_of, int n_neighbors,
                        const int32_t *full_nbr, int full_degree, int64_t batch, int64_t n_nodes,
@@ -480,6 +479,48 @@ __global__ void pack_full_kernel(int32_t *__restrict__ out, const int64_t *__res
 }  // namespace pa
 
 extern "C" int pa_cpu_heap_size_for(int ef_search) { return pa::cpu_heap_size_for(ef_search); }
+
+namespace pa {
+
+// Checks, then one launch on `stream` whose CTAs own pool slots
+// [slot_begin, slot_begin + slot_count).
+int refine_enqueue(int64_t *out_I, float *out_D, const int64_t *cand_I, const float *cand_D,
+                   const float *query, int64_t ldq, const float *storage_full,
+                   const int32_t *packed_nbr, const int32_t *row_of, int n_neighbors,
+                   const int32_t *full_nbr, int full_degree, int64_t batch, int64_t n_nodes,
+                   int d_model, int d_principle, int n_cand, int ef_search, int k, int stages,
+                   const pa_visited_pool *pool, int slot_begin, int slot_count, int32_t *stats,
+                   cudaStream_t stream) {
+    int rc = refine_check(out_I, out_D, cand_I, cand_D, query, ldq, storage_full, packed_nbr,
+                          row_of, n_neighbors, full_nbr, full_degree, batch, n_nodes, d_model,
+                          d_principle, n_cand, ef_search, k, stages);
+    if (rc != PA_OK || batch == 0) return rc;
+    if (pool == nullptr) return fail(PA_ERR_STATE, "visited pool is null");
+    uint8_t *marks; int32_t *epoch; int64_t slot_stride, pool_nodes; int n_slots;
+    pool_view(pool, &marks, &epoch, &slot_stride, &n_slots, &pool_nodes);
+    PA_REQUIRE(pool_nodes >= n_nodes, "the visited pool was created for fewer nodes");
+    PA_REQUIRE(slot_begin >= 0 && slot_count > 0 && slot_begin + slot_count <= n_slots,
+               "slot range outside the visited pool");
+    const RefineArgs A = refine_args(out_I, out_D, cand_I, cand_D, query, ldq, storage_full,
+                                     packed_nbr, row_of, n_neighbors, full_nbr, full_degree, batch,
+                                     n_nodes, d_model, d_principle, n_cand, ef_search, k, stages,
+                                     marks, epoch, slot_stride, slot_begin, stats);
+    return refine_launch(A, slot_count, stream);
+}
+
+}  // namespace pa
+
+extern "C" int pa_refine(int64_t *out_I, float *out_D, const int64_t *cand_I, const float *cand_D,
+                         const float *query, const float *storage_full, const int32_t *packed_nbr,
+                         const int32_t *row_of, int n_neighbors, const int32_t *full_nbr,
+                         int full_degree, int64_t batch, int64_t n_nodes, int d_model,
+                         int d_principle, int n_cand, int ef_search, int k, int stages,
+                         pa_visited_pool *pool, int32_t *stats, void *stream) {
+    return pa::refine_enqueue(out_I, out_D, cand_I, cand_D, query, d_model, storage_full,
+                              packed_nbr, row_of, n_neighbors, full_nbr, full_degree, batch,
+                              n_nodes, d_model, d_principle, n_cand, ef_search, k, stages, pool, 0,
+                              pa_visited_pool_slots(pool), stats, static_cast<cudaStream_t>(stream));
+}
 
 extern "C" int pa_pack_fullgraph(int32_t *full_nbr, const int64_t *indptr, const int64_t *indices,
                                  int64_t n_nodes, int degree, void *stream_) {

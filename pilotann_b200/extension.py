@@ -288,5 +288,95 @@ def search_reduced_noalloc(output_I, output_D, packed_nbr, row_of, storage, quer
             output_I.size(2), _stream(query.device)))
 
 
+def pack_fullgraph(indptr, indices, degree: int):
+    """The full graph as ``int32 [n_nodes, degree]`` rows, ``-1`` padded, from
+    upstream's CSR tensors (``fullgraph.indptr / indices``): what stage 3 of the
+    refinement walks.  A row ends at its first negative id; repeated ids are
+    dropped."""
+    _check_cuda("indptr", indptr, 1, torch.int64)
+    _check_cuda("indices", indices, 1, torch.int64)
+    n_nodes = indptr.size(0) - 1
+    out = torch.empty(n_nodes, degree, dtype=torch.int32, device=indptr.device)
+    with torch.cuda.device(indptr.device):
+        _C.check(_C.lib().pa_pack_fullgraph(out.data_ptr(), indptr.data_ptr(), indices.data_ptr(),
+                                            n_nodes, degree, _stream(indptr.device)))
+    return out
+
+
+class VisitedPool:
+    """``pa_visited_pool``: the device counterpart of upstream's ``BitmaskPool``
+    (``extension/inc/bitmask.hpp:51-76``) -- ``n_slots`` epoch-marked visited arrays
+    over ``n_nodes`` nodes, one per resident CTA of the refinement kernel."""
+
+    def __init__(self, n_nodes: int, n_slots: int, device=None):
+        import ctypes
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None \
+            else torch.device(device)
+        self.n_nodes, self.n_slots = n_nodes, n_slots
+        handle = ctypes.c_void_p()
+        with torch.cuda.device(self.device):
+            _C.check(_C.lib().pa_visited_pool_create(ctypes.byref(handle), n_nodes, n_slots))
+        self._h = handle
+
+    @staticmethod
+    def bytes_for(n_nodes: int, n_slots: int) -> int:
+        return int(_C.lib().pa_visited_pool_bytes(n_nodes, n_slots))
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            _C.lib().pa_visited_pool_destroy(self._h)
+            self._h = None
+
+    __del__ = close
+
+
+def cpu_heap_size_for(ef_search: int) -> int:
+    """Heap capacity of upstream's CPU search for ``ef_search``
+    (``extension/traverse_cpu.cpp:228-254``)."""
+    return int(_C.lib().pa_cpu_heap_size_for(ef_search))
+
+
+def refine(cand_I, cand_D, query, storage, packed_nbr, row_of, full_nbr, pool: VisitedPool,
+           ef_search: int, d_principle: int, k: int | None = None, stats=None):
+    """``traverse_refine`` (``extension/traverse_cpu.cpp:261-369``) on the GPU over
+    the candidate handoff ``cand_I / cand_D [B, 4, ef]`` (or ``[B, 4 * ef]``) in
+    device memory.  ``k=None`` runs the sub-graph stage alone and returns the
+    rewritten handoff rows ``[B, 4 * ef]`` (what upstream leaves in its buffer for
+    the full-graph stage); otherwise both stages run and ``(topk_I [B, k],
+    topk_D [B, k])`` comes back, ascending."""
+    B = query.size(0)
+    cand_I = cand_I.reshape(B, -1)
+    cand_D = cand_D.reshape(B, -1)
+    _check_cuda("cand_I", cand_I, 2, torch.int64)
+    _check_cuda("cand_D", cand_D, 2, torch.float32)
+    _check_cuda("query", query, 2, torch.float32)
+    _check_cuda("storage", storage, 2, torch.float32)
+    _check_cuda("packed_nbr", packed_nbr, 3, torch.int32)
+    _check_cuda("row_of", row_of, 1, torch.int32)
+    _require(cand_I.shape == cand_D.shape, "cand_I.sizes() == cand_D.sizes()")
+    _require(storage.size(1) == query.size(1), "storage.size(-1) == d_model")
+    _require(row_of.size(0) == storage.size(0), "row_of.size(0) == n_storage")
+    _require(packed_nbr.size(2) == 4, "packed_nbr.size(2) == 4")
+    _require(pool.n_nodes >= storage.size(0), "pool.n_nodes >= n_storage")
+    stages = 2 if k is None else 3
+    if stages == 3:
+        _check_cuda("full_nbr", full_nbr, 2, torch.int32)
+        _require(full_nbr.size(0) == storage.size(0), "full_nbr.size(0) == n_storage")
+    if stats is not None:
+        _check_cuda("stats", stats, 2, torch.int32)
+    n_out = cand_I.size(1) if k is None else k
+    out_I = torch.empty(B, n_out, dtype=torch.int64, device=query.device)
+    out_D = torch.empty(B, n_out, dtype=torch.float32, device=query.device)
+    with torch.cuda.device(query.device):
+        _C.check(_C.lib().pa_refine(
+            out_I.data_ptr(), out_D.data_ptr(), cand_I.data_ptr(), cand_D.data_ptr(),
+            query.data_ptr(), storage.data_ptr(), packed_nbr.data_ptr(), row_of.data_ptr(),
+            packed_nbr.size(1), 0 if full_nbr is None else full_nbr.data_ptr(),
+            0 if full_nbr is None else full_nbr.size(1), B, storage.size(0), query.size(1),
+            d_principle, cand_I.size(1), ef_search, 0 if k is None else k, stages, pool._h,
+            0 if stats is None else stats.data_ptr(), _stream(query.device)))
+    return out_I, out_D
+
+
 def launch_count() -> int:
     return int(_C.lib().pa_launch_count())

@@ -26,6 +26,7 @@ def make_problem(n: int = 4096, d: int = 64, n_nb: int = 32, ratio: float = 1.0,
         x, q = utils.make_storage(w), utils.make_queries(w)
     dev = torch.device(build_device)
     indptr, indices = utils.graph_init(x.to(dev), graph, n_nb)
+    full_indptr, full_indices = indptr, indices
     if ratio < 1.0:
         indptr, indices, nodelist, mapping = utils.subgraph_init(
             indptr, indices, x, graph, n_samples=int(ratio * n), n_neighbors=n_nb,
@@ -42,7 +43,7 @@ def make_problem(n: int = 4096, d: int = 64, n_nb: int = 32, ratio: float = 1.0,
         initial_D = initial_D * (1.0 + 0.01 * torch.rand(batch, n_init, generator=g))
     return dict(indptr=indptr, indices=indices, mapping=mapping, storage=storage, query=q,
                 initial_I=initial_I, initial_D=initial_D, n_neighbors=n_nb, full=x,
-                nodelist=nodelist)
+                nodelist=nodelist, full_indptr=full_indptr, full_indices=full_indices)
 
 
 def to_cuda(p: dict, device="cuda"):

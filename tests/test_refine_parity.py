@@ -1,0 +1,201 @@
+"""The refinement kernel (``pa_refine``: stage 2 on the sub-graph, stage 3 on the
+full graph, visited marks from the device pool) against
+
+* the CPU oracle restating upstream ``traverse_refine`` with THIS kernel's
+  summation order: ids, distance bits and per-stage counters identical;
+* upstream's own ``traverse_refine`` (AVX2 order, built with -ffast-math, so no
+  bit equality): top-k ids identical for at least 99.5 % of the queries,
+  distances within 1e-5 relative.
+
+The handoff both sides consume is produced by the traversal kernel of this
+package on the same tensors.
+"""
+import pytest
+import torch
+
+from helpers import make_problem, to_cuda
+
+pytestmark = pytest.mark.gpu
+
+
+def _case(n=12000, d=96, d_p=32, ratio=0.5, batch=256, ef=48, law="powerlaw", seed=41,
+          n_init=32):
+    """Handoff [B, 4*ef] from the reduced-space traversal + everything the
+    refinement needs, CPU and CUDA."""
+    from pilotann_b200 import extension
+    p = make_problem(n=n, d=d, ratio=ratio, batch=batch, n_init=n_init, seed=seed, law=law,
+                     build_device="cuda")
+    full = p["full"]
+    reduced = p["storage"][:, :d_p].contiguous()              # rows of the sampled nodes
+    q = p["query"]
+    q_red = q[:, :d_p].contiguous()
+    g = torch.Generator().manual_seed(seed)
+    ids = p["nodelist"][torch.randint(p["nodelist"].numel(), (batch, n_init), generator=g)]
+    diff = q_red.unsqueeze(1) - full[ids][:, :, :d_p]
+    init_D = (diff * diff).sum(-1).contiguous()
+    dev = "cuda"
+    nbr, row_of = extension.pack_graph(p["indptr"].to(dev), p["indices"].to(dev),
+                                       p["mapping"].to(dev), reduced.size(0), 32)
+    oI = torch.empty(batch, 4, ef, dtype=torch.int64, device=dev)
+    oD = torch.empty(batch, 4, ef, device=dev)
+    extension.traverse_packed(oI, oD, nbr, row_of, reduced.to(dev), q_red.to(dev), ids.to(dev),
+                              init_D.to(dev), 32)
+    full_nbr = extension.pack_fullgraph(p["full_indptr"].to(dev), p["full_indices"].to(dev), 32)
+    torch.cuda.synchronize()
+    return dict(p=p, nbr=nbr, row_of=row_of, full_nbr=full_nbr, hand_I=oI, hand_D=oD,
+                full=full, full_cuda=full.to(dev), q=q, q_cuda=q.to(dev), d_p=d_p, ef=ef)
+
+
+@pytest.mark.parametrize("ef,d,d_p,law", [(16, 64, 32, "fuzz"), (48, 96, 32, "powerlaw"),
+                                          (128, 200, 96, "powerlaw-ood"), (40, 64, 64, "mixture")])
+def test_both_stages_bit_exact_vs_oracle(oracle_lib, ef, d, d_p, law):
+    from pilotann_b200 import extension
+    c = _case(d=d, d_p=d_p, ef=ef, law=law, batch=192)
+    p = c["p"]
+    k = 10
+    pool = extension.VisitedPool(c["full"].size(0), 96)      # fewer slots than queries
+    sub = [p["indptr"], p["indices"]]
+    full = [p["full_indptr"], p["full_indices"]]
+    hI = c["hand_I"].reshape(192, -1).cpu()
+    hD = c["hand_D"].reshape(192, -1).cpu()
+    # stage 2 alone: the rewritten handoff rows
+    st = torch.zeros(192, 4, dtype=torch.int32, device="cuda")
+    g_I, g_D = extension.refine(c["hand_I"], c["hand_D"], c["q_cuda"], c["full_cuda"], c["nbr"],
+                                c["row_of"], None, pool, ef, d_p, k=None, stats=st)
+    w_bI, w_bD = hI.clone(), hD.clone()
+    _, _, w_st = oracle_lib.refine_ex(w_bI, w_bD, sub, full, c["full"], c["q"], k, ef, d_p,
+                                      gpu_order=True, stages=2, with_stats=True)
+    torch.cuda.synchronize()
+    assert torch.equal(g_I.cpu(), w_bI)
+    assert torch.equal(g_D.cpu().view(torch.int32), w_bD.view(torch.int32))
+    assert torch.equal(st.cpu()[:, :2], w_st[:, :2])
+    H = oracle_lib.cpu_heap_size_for(ef)
+    assert (g_I[:, : 4 * ef - H] == -1).all() and (g_I[:, -1] >= 0).float().mean() > 0.9
+    # both stages: top-k
+    st.zero_()
+    t_I, t_D = extension.refine(c["hand_I"], c["hand_D"], c["q_cuda"], c["full_cuda"], c["nbr"],
+                                c["row_of"], c["full_nbr"], pool, ef, d_p, k=k, stats=st)
+    w_I, w_D, w_st = oracle_lib.refine_ex(hI.clone(), hD.clone(), sub, full, c["full"], c["q"], k,
+                                          ef, d_p, gpu_order=True, stages=3, with_stats=True)
+    torch.cuda.synchronize()
+    assert torch.equal(t_I.cpu(), w_I)
+    assert torch.equal(t_D.cpu().view(torch.int32), w_D.view(torch.int32))
+    assert torch.equal(st.cpu(), w_st)
+    # the handoff itself was only read
+    assert torch.equal(c["hand_I"].reshape(192, -1).cpu(), hI)
+    # exact distances of what came back
+    exact = (c["q"].unsqueeze(1) - c["full"][w_I]).square().sum(-1)
+    assert torch.allclose(t_D.cpu(), exact, rtol=1e-4, atol=1e-6)
+
+
+def test_against_upstream_traverse_refine(ref_ext):
+    from pilotann_b200 import extension, utils
+    ef, k = 64, 10
+    c = _case(n=20000, d=128, d_p=32, ef=ef, law="powerlaw", batch=512, seed=43)
+    p = c["p"]
+    B = 512
+    pool = extension.VisitedPool(c["full"].size(0), 1024)
+    t_I, t_D = extension.refine(c["hand_I"], c["hand_D"], c["q_cuda"], c["full_cuda"], c["nbr"],
+                                c["row_of"], c["full_nbr"], pool, ef, c["d_p"], k=k)
+    torch.cuda.synchronize()
+    hI = c["hand_I"].reshape(B, -1).cpu().clone()
+    hD = c["hand_D"].reshape(B, -1).cpu().clone()
+    u_I = torch.empty(B, k, dtype=torch.int64)
+    u_D = torch.empty(B, k, dtype=torch.float32)
+    ref_ext.traverse_refine(u_I, u_D, hI, hD, hI, hD, [p["indptr"], p["indices"]],
+                            [p["full_indptr"], p["full_indices"]], c["full"], c["q"], ef, c["d_p"])
+    same = (t_I.cpu() == u_I).all(dim=1).float().mean().item()
+    print(f"top-{k} rows identical to upstream traverse_refine: {same:.4f}")
+    assert same >= 0.995
+    both = t_I.cpu() == u_I
+    rel = ((t_D.cpu() - u_D).abs() / u_D.abs().clamp_min(1e-30))[both]
+    assert rel.max().item() <= 1e-5
+    truth = utils.ground_truth(c["q"], c["full"], k)
+    assert abs(utils.recall(t_I.cpu(), truth) - utils.recall(u_I, truth)) <= 0.002
+    # stage 2 alone, then upstream's full-graph search on its rows: what a caller
+    # gets who keeps stage 3 on the CPU
+    s_I, s_D = extension.refine(c["hand_I"], c["hand_D"], c["q_cuda"], c["full_cuda"], c["nbr"],
+                                c["row_of"], None, pool, ef, c["d_p"], k=None)
+    v_I = torch.empty(B, k, dtype=torch.int64)
+    v_D = torch.empty(B, k, dtype=torch.float32)
+    ref_ext.traverse_cpu(v_I, v_D, s_I.cpu(), s_D.cpu(), p["full_indptr"], p["full_indices"],
+                         c["full"], c["q"], ef)
+    assert abs(utils.recall(v_I, truth) - utils.recall(u_I, truth)) <= 0.005
+    # after upstream's stage 2 the buffer holds exact full distances
+    # (test/kernel/test_traverse_refine.py:89-95 checks the same of upstream)
+    real = s_I.cpu() >= 0
+    exact = (c["q"].unsqueeze(1) - c["full"][s_I.cpu().clamp_min(0)]).square().sum(-1)
+    assert torch.allclose(s_D.cpu()[real], exact[real], rtol=1e-4, atol=1e-6)
+
+
+def test_marker_wrap_and_slot_reuse(oracle_lib):
+    """One slot serves 600 queries in a row: its marker passes 254 twice and the
+    array is wiped in between; results stay those of the oracle."""
+    from pilotann_b200 import extension
+    ef, k, B = 16, 5, 600
+    c = _case(n=6000, d=64, d_p=32, ef=ef, law="fuzz", batch=B, seed=47)
+    p = c["p"]
+    pool = extension.VisitedPool(c["full"].size(0), 1)
+    t_I, t_D = extension.refine(c["hand_I"], c["hand_D"], c["q_cuda"], c["full_cuda"], c["nbr"],
+                                c["row_of"], c["full_nbr"], pool, ef, c["d_p"], k=k)
+    torch.cuda.synchronize()
+    w_I, w_D = oracle_lib.refine_ex(c["hand_I"].reshape(B, -1).cpu().clone(),
+                                    c["hand_D"].reshape(B, -1).cpu().clone(),
+                                    [p["indptr"], p["indices"]],
+                                    [p["full_indptr"], p["full_indices"]], c["full"], c["q"], k,
+                                    ef, c["d_p"], gpu_order=True, stages=3)
+    assert torch.equal(t_I.cpu(), w_I)
+    assert torch.equal(t_D.cpu().view(torch.int32), w_D.view(torch.int32))
+
+
+def test_ragged_rows_pads_duplicates_and_sparse_handoff(oracle_lib):
+    """Rows cut short by -1, a repeated id inside a row, queries whose handoff is
+    mostly pads, ids outside the sample: the cases upstream's loops guard against
+    (traverse_cpu.cpp:47-49, 109-116)."""
+    from pilotann_b200 import extension
+    ef, k, B = 32, 10, 64
+    c = _case(n=6000, d=64, d_p=32, ef=ef, law="fuzz", batch=B, seed=53)
+    p = c["p"]
+    n = c["full"].size(0)
+    g = torch.Generator().manual_seed(9)
+    full_indices = p["full_indices"].clone().reshape(n, 32)
+    cut = torch.randint(n, (n // 3,), generator=g)
+    full_indices[cut, 20:] = -1                              # rows ending early
+    full_indices[cut[:500], 7] = full_indices[cut[:500], 3]  # a repeated id
+    full_indices = full_indices.reshape(-1).contiguous()
+    full_nbr = extension.pack_fullgraph(p["full_indptr"].cuda(), full_indices.cuda(), 32)
+    hI = c["hand_I"].reshape(B, -1).clone()
+    hD = c["hand_D"].reshape(B, -1).clone()
+    hI[:8, 5:] = -1                                          # almost empty handoffs
+    hD[:8, 5:] = float("inf")
+    hI[8:12] = -1                                            # nothing at all
+    pool = extension.VisitedPool(n, 16)
+    t_I, t_D = extension.refine(hI, hD, c["q_cuda"], c["full_cuda"], c["nbr"], c["row_of"],
+                                full_nbr, pool, ef, c["d_p"], k=k)
+    torch.cuda.synchronize()
+    w_I, w_D = oracle_lib.refine_ex(hI.cpu().clone(), hD.cpu().clone(),
+                                    [p["indptr"], p["indices"]],
+                                    [p["full_indptr"], full_indices], c["full"], c["q"], k, ef,
+                                    c["d_p"], gpu_order=True, stages=3)
+    assert torch.equal(t_I.cpu(), w_I)
+    assert torch.equal(t_D.cpu().view(torch.int32), w_D.view(torch.int32))
+    assert (t_I[8:12] == -1).all()
+
+
+def test_rejections():
+    from pilotann_b200 import _C
+    lib = _C.lib()
+    # stages must be 2 or 3
+    rc = lib.pa_refine(0, 0, 0, 0, 0, 0, 0, 0, 32, 0, 32, 4, 100, 64, 32, 64, 16, 10, 1, 0, 0, 0)
+    assert rc == _C.PA_ERR_ARG and b"stages" in lib.pa_last_error()
+    # k larger than the candidate row
+    rc = lib.pa_refine(0, 0, 0, 0, 0, 0, 0, 0, 32, 0, 32, 4, 100, 64, 32, 64, 16, 100, 3, 0, 0, 0)
+    assert rc == _C.PA_ERR_ARG and b"k must" in lib.pa_last_error()
+    # d_principle > d_model
+    rc = lib.pa_refine(0, 0, 0, 0, 0, 0, 0, 0, 32, 0, 32, 4, 100, 64, 96, 64, 16, 10, 3, 0, 0, 0)
+    assert rc == _C.PA_ERR_ARG
+    # a pool for fewer nodes is refused at creation of the call, and n_slots <= 0 at creation
+    import ctypes
+    h = ctypes.c_void_p()
+    assert lib.pa_visited_pool_create(ctypes.byref(h), 100, 0) == _C.PA_ERR_ARG
+    assert lib.pa_visited_pool_bytes(1000, 4) == 4 * 1008 + 16
