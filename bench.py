@@ -8,14 +8,20 @@ L2-normalised; 1024 queries from the same law; degree-32 graph, 25 % sampled
 sub-graph, d_principle = 128, router64x64 entries, top-10.  Synthetic stand-in
 for the public 768-d embedding sets, which are not available offline.
 
-A step is one pass of the GPU stage (projection, entry routing, traversal) over
-one 1024-query batch per GPU.  ``value`` times it with the raw queries already in
-HBM; ``e2e`` times the public host-buffer call (pinned host queries in, candidate
-handoff and rotated queries back in pinned host memory).  ef_search is the
-operating point at which the whole pipeline (this stage + upstream's CPU
-refinement) reaches recall@10 >= 0.90; the CPU leg re-measures that recall with
-upstream's own ``traverse_refine``.  With N > 1 every rank holds a replica of
-the index and its own 1024 queries (weak scaling, no data-path collective).
+A step is one pass of the whole search over one 1024-query batch per GPU:
+projection, entry routing, reduced-space traversal, refinement (sub-graph stage and
+full-graph stage of upstream's ``traverse_refine``, on the GPU) -- top-10 out.
+``value`` times it with the raw queries already in HBM (each step is the median
+of ten event-timed passes); ``e2e`` times the public host-buffer call (pinned host
+queries in, top-k back in pinned host memory).  ``stage`` carries the same two
+numbers for the part upstream runs on the GPU, i.e. up to the candidate handoff
+(the rotated queries and the handoff go back to the host there).  ef_search is
+the smallest value of upstream's sweep at which the search reaches recall@10 >=
+0.90 (``recall`` in the line is measured on the top-k the timed call returned; the
+CPU leg re-measures the pipeline with upstream's own ``traverse_refine`` as the
+consumer).  ``roofline`` describes the gather kernel that takes longer,
+``roofline_other_kernel`` the other one.  With N > 1 every rank holds a replica
+of the index and its own 1024 queries (weak scaling, no data-path collective).
 """
 from __future__ import annotations
 
@@ -42,9 +48,11 @@ TARGET_RECALL = 0.90
 # the recall it sees at this ef)
 OPERATING_EF = {1: 32, 2: 128, 3: 128}
 # ncu dram__bytes_read.sum + dram__bytes_write.sum per traversal launch divided by
-# the queries in that launch (bytes / query), from the capture summarised under
-# profiles/; None until captured
-NCU_TRAFFIC_PER_QUERY = {2: 1.497034e9 / 1024}   # profiles/traverse_kernel_c2-1m-768-cos_ef128.md
+# the queries in that launch (bytes / query), stamped with the state of the kernel
+# it was captured on; None until captured
+NCU_TRAFFIC_PER_QUERY = {2: {"bytes_per_query": 1.497034e9 / 1024,
+                             "captured_at": "commit 49677c7, library version 101"}}
+PASSES = 10       # event-timed passes per step; a step's time is their median
 FALLBACK_HBM_GBS = 6650.0
 
 
@@ -271,6 +279,16 @@ def cpu_baseline_leg(w, index, queries, truth, ef_gpu, repeats=3):
                                "refine_qps": round(q.size(0) / dt, 1)})
             if e == ef_gpu:
                 pipe = pipe_sweep[-1]
+                if ref is not None and index.stage.has_refine:
+                    # sub-graph stage on the GPU, upstream's full-graph search
+                    # (traverse_cpu) on the host from its rows
+                    sI, sD, rot2 = index.search_candidates(qp, e, stage2=True)
+                    t0 = time.perf_counter()
+                    ref.traverse_cpu(oI, oD, sI, sD, full[0], full[1], index.storage, rot2, e)
+                    dt2 = time.perf_counter() - t0
+                    pipe["gpu_stage2_then_upstream_stage3"] = {
+                        "recall": round(recall_at(oI, truth[:w.n_queries], k), 4),
+                        "refine_qps": round(q.size(0) / dt2, 1)}
     # upstream's own CUDA traversal kernel on this GPU, same tensors, same entries, at
     # the operating ef: the recompiled-reference number the kernel here is held against
     upstream_ms = None
@@ -298,7 +316,18 @@ def cpu_baseline_leg(w, index, queries, truth, ef_gpu, repeats=3):
         except Exception as exc:                     # a reported extra, never fatal
             upstream_ms = f"unavailable: {exc}"
     chosen = best or (sweep[-1] if sweep else {"ef": None, "recall": None, "qps": None})
-    return {"upstream_cuda_kernel_ms": upstream_ms,
+    at16 = None
+    if threads > 16 and chosen["ef"] is not None:
+        # the thread count upstream's published runs used (README.md:76-77)
+        import ctypes
+        ctypes.CDLL("libgomp.so.1").omp_set_num_threads(16)
+        times = [cpu_search(ref, index, rotated, EP_I, EP_D, k, chosen["ef"], 16)[1]
+                 for _ in range(repeats + 1)][1:]
+        at16 = {"cores": 16, "qps": round(q.size(0) / statistics.median(times), 1)}
+        ctypes.CDLL("libgomp.so.1").omp_set_num_threads(threads)
+    elif chosen["ef"] is not None:
+        at16 = {"cores": threads, "qps": chosen["qps"], "note": "the host has no more cores"}
+    return {"upstream_cuda_kernel_ms": upstream_ms, "at_16_threads": at16,
             "value": chosen["qps"], "unit": "queries/s", "cores": threads, "kind": kind,
             "sample": f"{q.size(0)} queries, upstream traverse_cpu on the full graph, ef sweep "
                       f"until recall@{k}>={TARGET_RECALL}, median of {repeats}",
@@ -396,6 +425,44 @@ def parity_leg(w, index, red, EP_I, EP_D, out_I, out_D, stats, ef, runs=5):
     return rec
 
 
+def refine_parity_leg(w, index, rot, hand_I, hand_D, top_I, top_D, r_stats, ef):
+    """The refinement kernel on the benchmark's own handoff: against the oracle
+    (traverse_refine restated with the kernel's summation order; bit for bit) and
+    against upstream's traverse_refine on the host (AVX2 order: ids and a relative
+    distance bound)."""
+    import oracle
+    k = w.top_k
+    B = rot.size(0)
+    sub = [index.subgraph.indptr, index.subgraph.indices]
+    full = [index.fullgraph.indptr, index.fullgraph.indices]
+    hI = hand_I.reshape(B, -1).cpu()
+    hD = hand_D.reshape(B, -1).cpu()
+    rot_c = rot.cpu()
+    t0 = time.perf_counter()
+    w_I, w_D, w_st = oracle.refine_ex(hI.clone(), hD.clone(), sub, full, index.storage, rot_c, k,
+                                      ef, w.d_principle, gpu_order=True, stages=3,
+                                      with_stats=True)
+    g_I, g_D = top_I.cpu(), top_D.cpu()
+    rec = {"oracle_bit_exact": bool(torch.equal(g_I, w_I)
+                                    and torch.equal(g_D.view(torch.int32), w_D.view(torch.int32))
+                                    and torch.equal(r_stats.cpu(), w_st)),
+           "oracle_seconds": round(time.perf_counter() - t0, 1)}
+    ref = load_reference()
+    if ref is None:
+        rec["upstream"] = "unavailable: upstream module not built"
+        return rec
+    u_I = torch.empty(B, k, dtype=torch.int64)
+    u_D = torch.empty(B, k, dtype=torch.float32)
+    bI, bD = hI.clone(), hD.clone()
+    ref.traverse_refine(u_I, u_D, bI, bD, bI, bD, sub, full, index.storage, rot_c, ef,
+                        w.d_principle)
+    same = g_I == u_I
+    rec["topk_rows_identical_to_upstream"] = float(same.all(dim=1).float().mean())
+    rel = ((g_D - u_D).abs() / u_D.abs().clamp_min(1e-30))[same]
+    rec["max_rel_distance_err"] = float(rel.max()) if rel.numel() else None
+    return rec
+
+
 # ---------------------------------------------------------------------- main
 
 def flush_l2(buf):
@@ -439,7 +506,9 @@ def main():
     if args.impl == "reference":
         base = cpu_baseline_leg(w, index, queries, truth, ef, repeats=max(3, steps // 4))
         line = {"impl": "reference", "metric": "QPS at recall@10>=0.90", "value": base["value"],
-                "unit": "queries/s", "n_gpus": args.gpus, "steps": steps, "warmup": warmup,
+                "unit": "queries/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+                "note": "the reference's CPU search runs on rank 0 alone with every host core"
+                        + (f"; launched with --gpus {args.gpus}" if args.gpus > 1 else ""),
                 "ms_per_step": None if not base["value"] else 1000.0 * B / base["value"],
                 "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                 "dtype": "f32", "data": "synthetic", "config": {**config, "ef_search": base["ef"]},
@@ -450,13 +519,18 @@ def main():
         return 0
 
     from pilotann_b200 import extension
-    index.to(device, max_batch=B, max_ef=max(EF_SWEEP))
+    index.to(device, max_batch=B, max_ef=max(EF_SWEEP), refine="gpu")
     stage = index.stage
+    k = w.top_k
     # every rank searches its own queries
-    q_host = queries[(rank % 8) * B:(rank % 8 + 1) * B].contiguous().pin_memory()
+    q_lo = (rank % 8) * B
+    q_host = queries[q_lo:q_lo + B].contiguous().pin_memory()
+    my_truth = truth[q_lo:q_lo + B]
     q_dev = q_host.to(device)
     out_I = torch.empty(B, 4, ef, dtype=torch.int64, device=device)
     out_D = torch.empty(B, 4, ef, dtype=torch.float32, device=device)
+    top_I = torch.empty(B, k, dtype=torch.int64, device=device)
+    top_D = torch.empty(B, k, dtype=torch.float32, device=device)
     stats = torch.zeros(B, 4, dtype=torch.int32, device=device)
     flush = torch.empty(512 << 20, dtype=torch.uint8, device=device)
     stream = stage.stream
@@ -467,77 +541,122 @@ def main():
             torch.distributed.barrier()
         torch.cuda.synchronize(device)
 
+    def timed_passes(call, on_stream, n_steps, n_passes):
+        """n_steps x n_passes event-timed passes of `call`, L2 flushed before each;
+        returns the per-pass times grouped by step."""
+        out = []
+        for _ in range(n_steps):
+            row = []
+            for _ in range(n_passes):
+                flush_l2(flush)
+                torch.cuda.synchronize(device)
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(on_stream)
+                call()
+                b.record(on_stream)
+                # the next pass's L2 flush runs on another stream: it must not start
+                # while this pass's kernels are still running
+                torch.cuda.synchronize(device)
+                row.append(a.elapsed_time(b))
+            out.append(row)
+        return out
+
+    def search_call():      # the whole search: raw queries in HBM -> top-k in HBM
+        stage.search_device(q_dev, ef, top_I, top_D, k=k)
+
+    def stage_call():       # the GPU stage of upstream's pipeline: -> candidate handoff
+        stage.search_device(q_dev, ef, out_I, out_D)
+
     # ---- value: inputs resident in HBM, CUDA events on the stage's stream ----
     # the clock sampler starts before the warm-up so that the GPU never idles
     # between the warm-up and the timed steps
-    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
-          for _ in range(steps)]
     sampler = ClockSampler(local)
     with sampler:
-        for _ in range(warmup):
-            flush_l2(flush)
-            torch.cuda.synchronize(device)
-            stage.search_device(q_dev, ef, out_I, out_D)
-            stage.synchronize()
+        timed_passes(search_call, stream, 1, warmup)
+        timed_passes(stage_call, stream, 1, warmup)
         launches0 = extension.launch_count()
         barrier()
-        for a, b in ev:
-            flush_l2(flush)
-            torch.cuda.synchronize(device)
-            a.record(stream)
-            stage.search_device(q_dev, ef, out_I, out_D)
-            b.record(stream)
-            # the next step's L2 flush runs on another stream: it must not start
-            # while this step's kernels are still running
-            torch.cuda.synchronize(device)
+        search_ms = timed_passes(search_call, stream, steps, PASSES)
         barrier()
-    launches = extension.launch_count() - launches0
-    step_ms = [a.elapsed_time(b) for a, b in ev]
+        launches = extension.launch_count() - launches0
+        stage_ms = timed_passes(stage_call, stream, steps, PASSES)
+    step_ms = [statistics.median(r) for r in search_ms]
     total_ms = sum(step_ms)
+    stage_step_ms = [statistics.median(r) for r in stage_ms]
+    recall = recall_at(top_I.cpu(), my_truth, k)
 
     # ---- e2e: the host-buffer call, wall clock around the blocking call ----
+    h_top_I = torch.empty(B, k, dtype=torch.int64, pin_memory=True)
+    h_top_D = torch.empty(B, k, dtype=torch.float32, pin_memory=True)
     n = 4 * ef
     h_I = torch.empty(B, n, dtype=torch.int64, pin_memory=True)
     h_D = torch.empty(B, n, dtype=torch.float32, pin_memory=True)
     h_rot = torch.empty(B, w.d_model, dtype=torch.float32, pin_memory=True)
-    for _ in range(warmup):
-        stage.search_host(q_host, ef, out_I=h_I, out_D=h_D, rotated=h_rot)
-    e2e_s = 0.0
-    barrier()
-    for _ in range(steps):
-        flush_l2(flush)
-        torch.cuda.synchronize(device)
-        t0 = time.perf_counter()
-        stage.search_host(q_host, ef, out_I=h_I, out_D=h_D, rotated=h_rot)
-        e2e_s += time.perf_counter() - t0
-    barrier()
-    h2d = q_host.numel() * 4
-    d2h = h_I.numel() * 8 + h_D.numel() * 4 + h_rot.numel() * 4
 
-    # ---- roofline: the traversal kernel alone, same inputs ----
+    def e2e_time(call):
+        for _ in range(warmup):
+            call()
+        total = 0.0
+        barrier()
+        for _ in range(steps):
+            flush_l2(flush)
+            torch.cuda.synchronize(device)
+            t0 = time.perf_counter()
+            call()
+            total += time.perf_counter() - t0
+        barrier()
+        return total
+
+    e2e_s = e2e_time(lambda: stage.search_host(q_host, ef, out_I=h_top_I, out_D=h_top_D, k=k))
+    e2e_chunked_s = e2e_time(lambda: stage.search_host(q_host, ef, chunk=256, out_I=h_top_I,
+                                                       out_D=h_top_D, k=k))
+    e2e_stage_s = e2e_time(lambda: stage.search_host(q_host, ef, out_I=h_I, out_D=h_D,
+                                                     rotated=h_rot))
+    e2e_stage_chunked_s = e2e_time(lambda: stage.search_host(q_host, ef, chunk=256, out_I=h_I,
+                                                             out_D=h_D, rotated=h_rot))
+    h2d = q_host.numel() * 4
+    d2h = h_top_I.numel() * 8 + h_top_D.numel() * 4
+    d2h_stage = h_I.numel() * 8 + h_D.numel() * 4 + h_rot.numel() * 4
+
+    # ---- rooflines: each gather kernel alone, same inputs ----
     rot = extension.project(q_dev, index.VT_cuda)
     red = rot[:, :w.d_principle].contiguous()
     EP_I, EP_D = index.entry.search(red)
-    t_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
-            for _ in range(steps)]
     cur = torch.cuda.current_stream(device)
-    for i in range(warmup + steps):
-        flush_l2(flush)
-        torch.cuda.synchronize(device)
-        if i >= warmup:
-            t_ev[i - warmup][0].record(cur)
+
+    def traverse_call():
         extension.traverse_packed(out_I, out_D, index.packed_nbr, index.row_of,
                                   index.storage_cuda, red, EP_I, EP_D, index.n_neighbors,
                                   stats=stats)
-        if i >= warmup:
-            t_ev[i - warmup][1].record(cur)
-    torch.cuda.synchronize(device)
-    trav_ms = statistics.mean(a.elapsed_time(b) for a, b in t_ev)
+
+    timed_passes(traverse_call, cur, 1, warmup)
+    trav_ms = statistics.mean(sum(timed_passes(traverse_call, cur, max(2, steps // 2), 5), []))
     st = stats.cpu().long()
     E, C = int(st[:, 1].sum()), int(st[:, 2].sum())
     n_init = EP_I.size(1)
     algo_bytes = (C * 4 * w.d_principle + E * 4 * index.n_neighbors
                   + B * (4 * w.d_principle + 12 * n_init + 48 * ef))
+    pool = extension.VisitedPool(index.storage.size(0), min(B, 1036), device)
+    r_stats = torch.zeros(B, 4, dtype=torch.int32, device=device)
+
+    def refine_call():
+        extension.refine(out_I, out_D, rot, index.storage_full_cuda, index.packed_nbr,
+                         index.row_of, index.full_nbr, pool, ef, w.d_principle, k=k,
+                         stats=r_stats, out=(top_I, top_D))
+
+    timed_passes(refine_call, cur, 1, warmup)
+    ref_ms = statistics.mean(sum(timed_passes(refine_call, cur, max(2, steps // 2), 5), []))
+    rs = r_stats.cpu().long()
+    n_cand = int((out_I >= 0).sum())
+    deg_full = index.full_nbr.size(1)
+    # candidates x residual dims + adjacency rows of the expanded nodes + full rows
+    # of the evaluated neighbours + one visited byte per neighbour looked at + the
+    # query, the handoff read and the top-k written
+    ref_bytes = (n_cand * 4 * (w.d_model - w.d_principle)
+                 + int(rs[:, 0].sum()) * 4 * index.n_neighbors + int(rs[:, 2].sum()) * 4 * deg_full
+                 + int(rs[:, 1].sum() + rs[:, 3].sum()) * 4 * w.d_model
+                 + int(rs[:, 0].sum()) * index.n_neighbors + int(rs[:, 2].sum()) * deg_full
+                 + B * (4 * w.d_model + 12 * 4 * ef + 12 * k))
     peak = FALLBACK_HBM_GBS
     peak_src = "fallback"
     peaks_file = ROOT / "MEASURED_PEAKS.json"
@@ -548,36 +667,72 @@ def main():
         except Exception:
             pass
     achieved = algo_bytes / (trav_ms * 1e-3) / 1e9
-    traffic_pq = NCU_TRAFFIC_PER_QUERY.get(cfg)
+    ref_achieved = ref_bytes / (ref_ms * 1e-3) / 1e9
+    traffic = NCU_TRAFFIC_PER_QUERY.get(cfg)
 
     # ---- max over ranks ----
-    times = torch.tensor([total_ms, e2e_s * 1e3], dtype=torch.float64, device=device)
+    times = torch.tensor([total_ms, e2e_s * 1e3, sum(stage_step_ms), e2e_chunked_s * 1e3,
+                          e2e_stage_s * 1e3, e2e_stage_chunked_s * 1e3],
+                         dtype=torch.float64, device=device)
     if world > 1:
         torch.distributed.all_reduce(times, op=torch.distributed.ReduceOp.MAX)
-    total_ms, e2e_ms = times.tolist()
+    total_ms, e2e_ms, stage_total_ms, e2e_chunked_ms, e2e_stage_ms, e2e_stage_chunked_ms = \
+        times.tolist()
     if rank != 0:
         torch.distributed.destroy_process_group()
         return 0
 
+    def qps(ms):
+        return world * B * steps / (ms * 1e-3)
+
+    all_passes = sum(search_ms, [])
+    trav = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+            "frac": achieved / peak, "peak_source": peak_src,
+            "traffic": None if traffic is None else traffic["bytes_per_query"] * B,
+            "traffic_captured_at": None if traffic is None else traffic["captured_at"],
+            "kernel": "traverse_kernel<H,PackedLayout>", "kernel_ms": trav_ms,
+            "algorithmic_bytes_per_launch": algo_bytes,
+            "expansions_per_query": E / B, "evaluations_per_query": C / B}
+    refn = {"bound": "hbm", "achieved": ref_achieved, "peak": peak, "unit": "GB/s",
+            "frac": ref_achieved / peak, "peak_source": peak_src,
+            "traffic": None, "kernel": "refine_kernel", "kernel_ms": ref_ms,
+            "algorithmic_bytes_per_launch": ref_bytes, "candidates_per_query": n_cand / B,
+            "stage2_expansions_per_query": float(rs[:, 0].sum()) / B,
+            "stage2_evaluations_per_query": float(rs[:, 1].sum()) / B,
+            "stage3_expansions_per_query": float(rs[:, 2].sum()) / B,
+            "stage3_evaluations_per_query": float(rs[:, 3].sum()) / B}
+    dominant, other = (trav, refn) if trav_ms >= ref_ms else (refn, trav)
     line = {
-        "metric": "QPS at recall@10>=0.90", "value": world * B * steps / (total_ms * 1e-3),
+        "metric": "QPS at recall@10>=0.90", "value": qps(total_ms),
         "unit": "queries/s", "n_gpus": world, "steps": steps, "warmup": warmup,
         "ms_per_step": total_ms / steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
-        "e2e": {"value": world * B * steps / (e2e_ms * 1e-3), "unit": "queries/s",
-                "h2d_bytes_per_step": world * h2d, "d2h_bytes_per_step": world * d2h},
-        "gpu_launches": launches,
-        "step_ms": {"min": min(step_ms), "median": statistics.median(step_ms), "max": max(step_ms)},
+        "what": "whole search on the GPU: projection, entry routing, reduced-space traversal, "
+                "refinement (sub-graph stage and full-graph stage), top-k out",
+        "recall": round(recall, 4),
+        "e2e": {"value": qps(e2e_ms), "unit": "queries/s", "h2d_bytes_per_step": world * h2d,
+                "d2h_bytes_per_step": world * d2h, "chunk": 0,
+                "chunk_256": {"value": qps(e2e_chunked_ms)}},
+        "gpu_launches": launches, "passes_per_step": PASSES,
+        "step_ms": {"min": min(step_ms), "median": statistics.median(step_ms),
+                    "max": max(step_ms)},
+        "pass_ms": {"min": min(all_passes), "median": statistics.median(all_passes),
+                    "max": max(all_passes)},
         "clocks": sampler.summary(),
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "peak_source": peak_src,
-                     "traffic": None if traffic_pq is None else traffic_pq * B,
-                     "kernel": "traverse_kernel<H,PackedLayout>", "kernel_ms": trav_ms,
-                     "algorithmic_bytes_per_launch": algo_bytes,
-                     "expansions_per_query": E / B, "evaluations_per_query": C / B},
+        "roofline": dominant, "roofline_other_kernel": other,
+        # the GPU stage of upstream's pipeline alone (candidate handoff out): the
+        # part upstream runs on the GPU, its CPU refinement not included
+        "stage": {"value": qps(stage_total_ms), "unit": "queries/s",
+                  "ms_per_step": stage_total_ms / steps,
+                  "e2e": {"value": qps(e2e_stage_ms), "h2d_bytes_per_step": world * h2d,
+                          "d2h_bytes_per_step": world * d2h_stage,
+                          "chunk_256": {"value": qps(e2e_stage_chunked_ms)}}},
     }
     if world == 1 and not args.no_cpu:
+        traverse_call()
         line["parity"] = parity_leg(w, index, red, EP_I, EP_D, out_I, out_D, stats, ef)
+        line["parity"]["refine"] = refine_parity_leg(w, index, rot, out_I, out_D, top_I, top_D,
+                                                     r_stats, ef)
         line["cpu_baseline"] = cpu_baseline_leg(w, index, queries, truth, ef)
     if world > 1:
         torch.distributed.destroy_process_group()

@@ -23,8 +23,17 @@ SYMBOLS = (
     "pa_launch_count", "pa_search_reduced_noalloc", "pa_device_status", "pa_route_ws", "pa_route_workspace_floats",
     "pa_selftest_bounded_wait", "pa_visited_pool_bytes", "pa_visited_pool_create",
     "pa_visited_pool_destroy", "pa_visited_pool_slots", "pa_cpu_heap_size_for",
-    "pa_pack_fullgraph", "pa_refine",
+    "pa_pack_fullgraph", "pa_refine", "pa_stage_attach_refine", "pa_stage_search_ex",
+    "pa_stage_search_device_ex", "pa_stage_slot_rows", "pa_stage_submit", "pa_stage_wait",
 )
+
+PA_OUT_HANDOFF, PA_OUT_STAGE2, PA_OUT_TOPK = 0, 1, 2
+
+
+class RefineIndex(Structure):
+    """``pa_refine_index``"""
+    _fields_ = [("storage_full", c_void_p), ("full_nbr", c_void_p), ("full_degree", c_int)]
+
 
 
 class StageIndex(Structure):
@@ -89,6 +98,18 @@ def lib() -> ctypes.CDLL:
     L.pa_refine.argtypes = [P, P, P, P, P, P, P, P, c_int, P, c_int, c_int64, c_int64, c_int,
                             c_int, c_int, c_int, c_int, c_int, P, P, P]
     L.pa_refine.restype = c_int
+    L.pa_stage_attach_refine.argtypes = [P, POINTER(RefineIndex), c_int]
+    L.pa_stage_attach_refine.restype = c_int
+    L.pa_stage_search_ex.argtypes = [P, P, P, P, P, c_int64, c_int, c_int, c_int, c_int64]
+    L.pa_stage_search_ex.restype = c_int
+    L.pa_stage_search_device_ex.argtypes = [P, P, P, P, c_int64, c_int, c_int, c_int, P, P]
+    L.pa_stage_search_device_ex.restype = c_int
+    L.pa_stage_slot_rows.argtypes = [P]
+    L.pa_stage_slot_rows.restype = c_int64
+    L.pa_stage_submit.argtypes = [P, c_int, P, c_int64, c_int, c_int, c_int, c_int]
+    L.pa_stage_submit.restype = c_int
+    L.pa_stage_wait.argtypes = [P, c_int, POINTER(P), POINTER(P), POINTER(P), POINTER(c_int64)]
+    L.pa_stage_wait.restype = c_int
     L.pa_selftest_bounded_wait.argtypes = [P]
     L.pa_selftest_bounded_wait.restype = c_int
     L.pa_device_status.argtypes = [c_int]

@@ -5,5 +5,6 @@ behind the ``pilot_ann`` Python surface: ``kernels`` (op wrappers), ``layers``
 (``include/pilotann_b200.h``); there is no CPU fallback."""
 from . import utils, extension, kernels, layers, stage, sharding  # noqa: F401
 from .stage import SearchStage  # noqa: F401
+from .extension import set_refine, get_refine  # noqa: F401
 
 __version__ = "0.1.0"

@@ -337,7 +337,7 @@ def cpu_heap_size_for(ef_search: int) -> int:
 
 
 def refine(cand_I, cand_D, query, storage, packed_nbr, row_of, full_nbr, pool: VisitedPool,
-           ef_search: int, d_principle: int, k: int | None = None, stats=None):
+           ef_search: int, d_principle: int, k: int | None = None, stats=None, out=None):
     """``traverse_refine`` (``extension/traverse_cpu.cpp:261-369``) on the GPU over
     the candidate handoff ``cand_I / cand_D [B, 4, ef]`` (or ``[B, 4 * ef]``) in
     device memory.  ``k=None`` runs the sub-graph stage alone and returns the
@@ -365,8 +365,14 @@ def refine(cand_I, cand_D, query, storage, packed_nbr, row_of, full_nbr, pool: V
     if stats is not None:
         _check_cuda("stats", stats, 2, torch.int32)
     n_out = cand_I.size(1) if k is None else k
-    out_I = torch.empty(B, n_out, dtype=torch.int64, device=query.device)
-    out_D = torch.empty(B, n_out, dtype=torch.float32, device=query.device)
+    if out is None:
+        out_I = torch.empty(B, n_out, dtype=torch.int64, device=query.device)
+        out_D = torch.empty(B, n_out, dtype=torch.float32, device=query.device)
+    else:
+        out_I, out_D = out
+        _check_cuda("out_I", out_I, 2, torch.int64)
+        _check_cuda("out_D", out_D, 2, torch.float32)
+        _require(out_I.shape == (B, n_out) and out_D.shape == (B, n_out), "out shape [B, n_out]")
     with torch.cuda.device(query.device):
         _C.check(_C.lib().pa_refine(
             out_I.data_ptr(), out_D.data_ptr(), cand_I.data_ptr(), cand_D.data_ptr(),
@@ -376,6 +382,176 @@ def refine(cand_I, cand_D, query, storage, packed_nbr, row_of, full_nbr, pool: V
             d_principle, cand_I.size(1), ef_search, 0 if k is None else k, stages, pool._h,
             0 if stats is None else stats.data_ptr(), _stream(query.device)))
     return out_I, out_D
+
+
+# ---- pipeline -------------------------------------------------------------------
+# Who consumes the candidate handoff in `pipeline` (and in IndexStaged.search):
+#   "gpu"      the refinement kernel of this package (default): candidates never
+#              leave the device, the call returns the final top-k;
+#   callable   a CPU consumer with the signature of upstream's
+#              extension.traverse_refine (extension/entry.cpp:39-46), e.g. that very
+#              function: it refines chunk i-2 while the GPU traverses chunk i-1, as
+#              upstream's pipeline does;
+#   None       no consumer: pipeline raises.
+_refine_consumer = "gpu"
+
+
+def set_refine(consumer) -> None:
+    """Chooses the consumer of the candidate handoff: ``"gpu"``, a callable with
+    upstream's ``traverse_refine`` signature, or ``None``."""
+    global _refine_consumer
+    if consumer is not None and consumer != "gpu" and not callable(consumer):
+        raise RuntimeError('set_refine: pass "gpu", a callable, or None')
+    _refine_consumer = consumer
+
+
+def get_refine():
+    return _refine_consumer
+
+
+_pipe_lock = threading.Lock()
+_pipe_buffers: dict = {}      # (device, chunk, ef, k) -> persistent stream / buffer set
+_resident: dict = {}          # device-resident forms of a caller's CPU index tensors
+_N_PIPE_STREAMS = 2           # N_PREFETCH of upstream (extension/pipeline_cpu.cpp:5)
+
+
+def _pipe_set(dev: torch.device, chunk: int, ef: int, k: int):
+    """Streams, device handoff buffers and pinned host buffers of `pipeline`, made
+    once per shape and kept (upstream allocates them in every call,
+    ``extension/pipeline_cpu.cpp:78-96``)."""
+    key = (dev.index if dev.index is not None else torch.cuda.current_device(), chunk, ef, k)
+    with _pipe_lock:
+        bs = _pipe_buffers.get(key)
+        if bs is None:
+            while len(_pipe_buffers) >= 4:
+                _pipe_buffers.pop(next(iter(_pipe_buffers)))
+            n = _N_PIPE_STREAMS
+            bs = {
+                "streams": [torch.cuda.Stream(device=dev) for _ in range(n)],
+                "dev_I": [torch.empty(chunk, 4, ef, dtype=torch.int64, device=dev) for _ in range(n)],
+                "dev_D": [torch.empty(chunk, 4, ef, dtype=torch.float32, device=dev) for _ in range(n)],
+                "host_I": [torch.empty(chunk, 4 * ef, dtype=torch.int64, pin_memory=True)
+                           for _ in range(n)],
+                "host_D": [torch.empty(chunk, 4 * ef, dtype=torch.float32, pin_memory=True)
+                           for _ in range(n)],
+                "top_I": [torch.empty(chunk, k, dtype=torch.int64, device=dev) for _ in range(n)],
+                "top_D": [torch.empty(chunk, k, dtype=torch.float32, device=dev) for _ in range(n)],
+            }
+            _pipe_buffers[key] = bs
+    return bs
+
+
+def _resident_for(graph, storage, subgraph_cuda, n_storage_sub: int, n_neighbors: int,
+                  chunk: int, dev: torch.device):
+    """Device-resident forms of the tensors upstream's CPU refinement reads: the
+    full-dimension vectors, the full graph packed to int32 rows, the packed
+    sub-graph, and one visited pool per side stream.  Built the first time a set of
+    tensor objects is seen (an upload of the whole vector table: the counterpart of
+    ``IndexStaged.to``), kept while they live."""
+    import weakref
+    tensors = (graph[0], graph[1], storage, *subgraph_cuda)
+    key = tuple(t.data_ptr() for t in tensors) + (dev.index, n_neighbors)
+    stamp = tuple(t._version for t in tensors)
+    with _pipe_lock:
+        for dead in [kk for kk, e in _resident.items() if any(r() is None for r in e["refs"])]:
+            del _resident[dead]
+        entry = _resident.get(key)
+        if entry is not None and entry["stamp"] == stamp and \
+                all(r() is t for r, t in zip(entry["refs"], tensors)) and entry["chunk"] >= chunk:
+            return entry
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("pipeline: the first call with a new index uploads it; make that "
+                               "call outside stream capture")
+        while len(_resident) >= 2:
+            _resident.pop(next(iter(_resident)))
+        degree = int((graph[0][1:] - graph[0][:-1]).max().item()) if graph[0].numel() > 1 else 1
+        degree = max(32, (degree + 31) // 32 * 32)
+        packed = pack_graph(subgraph_cuda[0], subgraph_cuda[1], subgraph_cuda[2], n_storage_sub,
+                            n_neighbors)
+        full_nbr = pack_fullgraph(graph[0].to(dev), graph[1].to(dev), degree)
+        entry = {"refs": tuple(weakref.ref(t) for t in tensors), "stamp": stamp, "chunk": chunk,
+                 "packed": packed, "full_nbr": full_nbr,
+                 "storage": storage.to(dev).contiguous(),
+                 "pools": [VisitedPool(storage.size(0), min(chunk, 1036), dev)
+                           for _ in range(_N_PIPE_STREAMS)]}
+        _resident[key] = entry
+        return entry
+
+
+def pipeline(graph, subgraph, subgraph_cuda, storage, storage_cuda, query, query_cuda,
+             initial_I, initial_D, n_neighbors: int, ef_search: int, d_principle: int, k: int,
+             chunk_size: int):
+    """``extension.pipeline`` with upstream's positional order
+    (``extension/entry.cpp:48-56``, ``extension/pipeline_cpu.cpp:32-145``): chunks
+    of ``chunk_size`` queries alternate over two side streams; returns
+    ``[topk_I int64 [B, k], topk_D f32 [B, k]]`` on the CPU, ascending.  Who turns
+    the candidates into the top-k is set by :func:`set_refine`."""
+    if len(graph) != 2 or len(subgraph) != 2 or len(subgraph_cuda) != 3:
+        raise RuntimeError("graph / subgraph / subgraph_cuda must hold 2 / 2 / 3 tensors")
+    _check_cuda("query_cuda", query_cuda, 2, torch.float32)
+    _check_cuda("storage_cuda", storage_cuda, 2, torch.float32)
+    batch = query.size(0)
+    _require(chunk_size > 0 and batch % chunk_size == 0, "batch_size % chunk_size == 0")
+    _require(query_cuda.size(0) == batch, "query_cuda.size(0) == batch_size")
+    consumer = _refine_consumer
+    if consumer is None:
+        raise RuntimeError("pipeline: no consumer for the candidate handoff; call "
+                           "pilotann_b200.set_refine(\"gpu\") or set_refine(<traverse_refine>)")
+    dev = query_cuda.device
+    n_streams = _N_PIPE_STREAMS
+    bs = _pipe_set(dev, chunk_size, ef_search, k)
+    streams = bs["streams"]
+    topk_I = torch.empty(batch, k, dtype=torch.int64, pin_memory=True)
+    topk_D = torch.empty(batch, k, dtype=torch.float32, pin_memory=True)
+    n_chunks = batch // chunk_size
+    ready = torch.cuda.Event()
+    ready.record(torch.cuda.current_stream(dev))      # the inputs were produced on this stream
+
+    def traverse(slot, lo, hi):
+        traverse_cuda(bs["dev_I"][slot], bs["dev_D"][slot], subgraph_cuda[0], subgraph_cuda[1],
+                      subgraph_cuda[2], storage_cuda, query_cuda[lo:hi], initial_I[lo:hi],
+                      initial_D[lo:hi], n_neighbors)
+
+    if consumer == "gpu":
+        res = _resident_for(graph, storage, subgraph_cuda, storage_cuda.size(0), n_neighbors,
+                            chunk_size, dev)
+        q_full = query.to(dev, non_blocking=True)
+        ready.record(torch.cuda.current_stream(dev))
+        for i in range(n_chunks):
+            slot = i % n_streams
+            lo, hi = i * chunk_size, (i + 1) * chunk_size
+            with torch.cuda.stream(streams[slot]):
+                streams[slot].wait_event(ready)
+                traverse(slot, lo, hi)
+                refine(bs["dev_I"][slot], bs["dev_D"][slot], q_full[lo:hi], res["storage"],
+                       res["packed"][0], res["packed"][1], res["full_nbr"], res["pools"][slot],
+                       ef_search, d_principle, k=k, out=(bs["top_I"][slot], bs["top_D"][slot]))
+                topk_I[lo:hi].copy_(bs["top_I"][slot], non_blocking=True)
+                topk_D[lo:hi].copy_(bs["top_D"][slot], non_blocking=True)
+        for s_ in streams:
+            s_.synchronize()
+        del q_full
+        return [topk_I, topk_D]
+
+    # a CPU consumer: chunk i is launched, then chunk i - n_streams (long finished on
+    # the GPU) is refined on the host while the GPU works on the chunks in between
+    for i in range(n_chunks + n_streams):
+        slot = i % n_streams
+        if i >= n_streams:
+            streams[slot].synchronize()
+            lo = (i - n_streams) * chunk_size
+            hi = lo + chunk_size
+            consumer(topk_I[lo:hi], topk_D[lo:hi], bs["host_I"][slot], bs["host_D"][slot],
+                     bs["host_I"][slot], bs["host_D"][slot], subgraph, graph, storage,
+                     query[lo:hi], ef_search, d_principle)
+        if i < n_chunks:
+            lo, hi = i * chunk_size, (i + 1) * chunk_size
+            with torch.cuda.stream(streams[slot]):
+                streams[slot].wait_event(ready)
+                traverse(slot, lo, hi)
+                bs["host_I"][slot].copy_(bs["dev_I"][slot].view(chunk_size, -1), non_blocking=True)
+                bs["host_D"][slot].copy_(bs["dev_D"][slot].view(chunk_size, -1), non_blocking=True)
+    return [topk_I, topk_D]
 
 
 def launch_count() -> int:

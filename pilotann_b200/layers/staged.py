@@ -94,11 +94,18 @@ class IndexStaged(nn.Module):
         return self
 
     # -- device residency (pilot_ann/layers/staged.py:124-139) -------------------
-    def to(self, device, max_batch: int = 4096, max_ef: int = 256, n_streams: int = 2):
+    def to(self, device, max_batch: int = 4096, max_ef: int = 256, n_streams: int = 2,
+           refine: str | None = "gpu", refine_slots: int = 0):
         """Uploads the reduced vectors of the sampled nodes, the entry tables,
         the rotation, and the sub-graph in the packed layout (per neighbour slot
         int32 id, storage row and bloom probes, indexed by storage row); creates
-        the per-device search stage."""
+        the per-device search stage.
+
+        ``refine="gpu"`` (default) also makes resident what ``traverse_refine``
+        reads on the CPU upstream -- the full-dimension vectors and the full graph
+        as int32 rows -- so that :meth:`search` can finish on the device;
+        ``refine="stage2"`` uploads the vectors only (the sub-graph stage on the GPU,
+        the full-graph search stays with a CPU consumer); ``None`` uploads neither."""
         device = torch.device(device)
         self.cuda_device = device
         self.entry.to(device=device)
@@ -118,32 +125,77 @@ class IndexStaged(nn.Module):
             entry_nodes=self.entry.entry_nodes, entry_vectors=self.entry.entry_vectors,
             n_neighbors=self.n_neighbors, d_model=self.d_model, max_batch=max_batch,
             max_ef=max_ef, n_streams=n_streams)
+        self.storage_full_cuda = self.full_nbr = None
+        if refine in ("gpu", "stage2"):
+            self.storage_full_cuda = self.storage.to(device).contiguous()
+            if refine == "gpu":
+                lengths = self.fullgraph.indptr[1:] - self.fullgraph.indptr[:-1]
+                degree = max(32, (int(lengths.max().item()) + 31) // 32 * 32)
+                self.full_nbr = extension.pack_fullgraph(self.fullgraph.indptr.to(device),
+                                                         self.fullgraph.indices.to(device), degree)
+            self.stage.attach_refine(self.storage_full_cuda, self.full_nbr, refine_slots)
+        elif refine is not None:
+            raise RuntimeError('refine must be "gpu", "stage2" or None')
         return self
 
     # -- search (pilot_ann/layers/staged.py:191-228) ------------------------------
     @torch.no_grad()
-    def search_candidates(self, query: torch.Tensor, ef_search: int, chunk_size: int = 0):
+    def search_candidates(self, query: torch.Tensor, ef_search: int, chunk_size: int = 0,
+                          stage2: bool = False):
         """The GPU stage alone: raw host queries in, candidate handoff out.
         Returns ``(handoff_I [B, 4*ef] int64, handoff_D [B, 4*ef] f32, rotated
         [B, d_model] f32)`` as pinned CPU tensors -- exactly what upstream hands
-        to ``traverse_refine`` (``extension/pipeline_cpu.cpp:110-117``)."""
+        to ``traverse_refine`` (``extension/pipeline_cpu.cpp:110-117``); with
+        ``stage2`` the rows after the sub-graph stage of the refinement (what
+        upstream's stage 3, ``traverse_cpu``, starts from)."""
         assert query.dim() == 2 and self.stage is not None
         query = query.contiguous()
         rotated = torch.empty(query.shape, dtype=torch.float32, pin_memory=True)
-        return self.stage.search_host(query, ef_search, chunk=chunk_size, rotated=rotated)
+        return self.stage.search_host(query, ef_search, chunk=chunk_size, rotated=rotated,
+                                      stage2=stage2)
 
     @torch.no_grad()
     def search(self, query: torch.Tensor, k: int, ef_search: int, chunk_size: int = 128,
                refine=None):
-        """Full search; ``refine`` is the CPU consumer of the handoff (upstream's
-        ``extension.traverse_refine``), which is not part of this package."""
-        if refine is None:
-            raise RuntimeError("search: pass refine=<upstream extension.traverse_refine>, or "
-                               "use search_candidates() for the GPU stage alone")
-        I, D, rotated = self.search_candidates(query, ef_search, chunk_size)
-        topk_I = torch.empty(query.size(0), k, dtype=torch.int64)
-        topk_D = torch.empty(query.size(0), k, dtype=torch.float32)
-        refine(topk_I, topk_D, I, D, I, D, [self.subgraph.indptr, self.subgraph.indices],
-               [self.fullgraph.indptr, self.fullgraph.indices], self.storage, rotated,
-               ef_search, self.d_principle)
+        """``IndexStaged.search`` (``pilot_ann/layers/staged.py:191-228``): raw host
+        queries in, ``(topk_I [B, k], topk_D [B, k])`` on the CPU out.
+
+        Who refines the candidates: ``refine`` if given, else what
+        :func:`pilotann_b200.set_refine` chose.  ``"gpu"`` finishes on the device
+        (needs ``to(..., refine="gpu")``).  A callable with the signature of
+        upstream's ``extension.traverse_refine`` runs on the host: chunks are
+        submitted to the stage's slots and the callable refines one chunk while the
+        GPU works on the next ones (upstream's overlap,
+        ``extension/pipeline_cpu.cpp:99-141``)."""
+        assert query.dim() == 2 and self.stage is not None
+        consumer = refine if refine is not None else extension.get_refine()
+        if consumer is None:
+            raise RuntimeError("search: no consumer for the candidate handoff; pass refine=, call "
+                               "pilotann_b200.set_refine, or use search_candidates()")
+        query = query.contiguous()
+        B = query.size(0)
+        if consumer == "gpu":
+            if not self.stage.has_full_graph:
+                raise RuntimeError('search: the index was moved to the device without '
+                                   'refine="gpu"; pass refine=<traverse_refine>')
+            I, D, _ = self.stage.search_host(query, ef_search, chunk=chunk_size, k=k)
+            return I, D
+        stage = self.stage
+        step = min(chunk_size if chunk_size > 0 else B, stage.slot_rows)
+        chunks = [(lo, min(B, lo + step)) for lo in range(0, B, step)]
+        topk_I = torch.empty(B, k, dtype=torch.int64)
+        topk_D = torch.empty(B, k, dtype=torch.float32)
+        sub = [self.subgraph.indptr, self.subgraph.indices]
+        full = [self.fullgraph.indptr, self.fullgraph.indices]
+        n_slots = stage.n_streams
+        for i in range(len(chunks) + n_slots):
+            slot = i % n_slots
+            if i >= n_slots:
+                lo, hi = chunks[i - n_slots]
+                hI, hD, rot = stage.wait(slot)
+                consumer(topk_I[lo:hi], topk_D[lo:hi], hI, hD, hI, hD, sub, full, self.storage,
+                         rot, ef_search, self.d_principle)
+            if i < len(chunks):
+                lo, hi = chunks[i]
+                stage.submit(slot, query[lo:hi], ef_search, want_rotated=True)
         return topk_I, topk_D

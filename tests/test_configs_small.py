@@ -52,3 +52,13 @@ def test_config_end_to_end(oracle_lib, cfg, ef, k, floor):
     assert utils.recall(I, truth) >= floor
     exact = torch.cdist(q.unsqueeze(1), x[I]).squeeze(1).square()
     assert torch.allclose(D, exact, atol=1e-3)
+    # the same search finished on the device (refinement kernel): the oracle's
+    # restatement in that kernel's summation order, bit for bit, and the recall of
+    # the CPU-refined run
+    gI, gD = index.search(q, k, ef)
+    w_I, w_D = oracle_lib.refine_ex(hI.clone(), hD.clone(),
+                                    [index.subgraph.indptr, index.subgraph.indices],
+                                    [index.fullgraph.indptr, index.fullgraph.indices],
+                                    index.storage, rot.clone(), k, ef, w.d_principle, gpu_order=True)
+    assert torch.equal(gI, w_I) and torch.equal(gD.view(torch.int32), w_D.view(torch.int32))
+    assert abs(utils.recall(gI, truth) - utils.recall(I, truth)) <= 0.002

@@ -167,9 +167,19 @@ def test_pipeline_drop_in_vs_upstream_pipeline(ref_ext):
     d_p = 96      # no reduction in this test: the whole vector is "principal"
     args = dict(storage=p["full"], storage_cuda=c["storage"], query=p["query"],
                 query_cuda=c["query"], initial_I=c["initial_I"], initial_D=c["initial_D"])
-    ours_I, ours_D = kernels.pipeline(graph=graph, subgraph=subgraph, subgraph_cuda=sub_cuda,
-                                      n_neighbors=32, k=k, ef_search=ef, d_principle=d_p,
-                                      chunk_size=chunk, refine=ref_ext.traverse_refine, **args)
+    import pilotann_b200
+    try:
+        pilotann_b200.set_refine(ref_ext.traverse_refine)     # upstream's own CPU consumer
+        ours_I, ours_D = kernels.pipeline(graph=graph, subgraph=subgraph, subgraph_cuda=sub_cuda,
+                                          n_neighbors=32, k=k, ef_search=ef, d_principle=d_p,
+                                          chunk_size=chunk, **args)
+    finally:
+        pilotann_b200.set_refine("gpu")
+    # and with this package's own consumer (the refinement kernel): the whole search
+    # on the device
+    gpu_I, gpu_D = kernels.pipeline(graph=graph, subgraph=subgraph, subgraph_cuda=sub_cuda,
+                                    n_neighbors=32, k=k, ef_search=ef, d_principle=d_p,
+                                    chunk_size=chunk, **args)
     def upstream():
         return ref_ext.pipeline(graph, subgraph, sub_cuda, args["storage"], args["storage_cuda"],
                                 args["query"], args["query_cuda"], args["initial_I"],
@@ -192,5 +202,10 @@ def test_pipeline_drop_in_vs_upstream_pipeline(ref_ext):
           f"(upstream run-to-run {jitter:.4f}, sigma {sigma:.4f})")
     assert abs(r_ours - r_theirs) <= 0.005
     assert miss <= max(0.005, 1.5 * jitter + 4.0 * sigma)
+    # GPU refinement against CPU refinement on the same (deterministic) handoff
+    same = 1.0 - mismatch(gpu_I, ours_I)
+    print(f"GPU-refined top-{k} rows equal to CPU-refined ones: {same:.4f}")
+    assert same >= 0.995
+    assert abs(utils.recall(gpu_I, truth) - r_ours) <= 0.002
     exact = torch.cdist(p["query"].unsqueeze(1), p["full"][ours_I]).squeeze(1).square()
     assert torch.allclose(ours_D, exact, atol=1e-3)

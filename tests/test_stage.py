@@ -106,21 +106,98 @@ def test_pipeline_wrapper_matches_upstream_signature(small_index, oracle_lib):
                                  query.contiguous(), out_I.size(1), ef_search, d_principle)
         out_I.copy_(I); out_D.copy_(D)
 
-    I, D = kernels.pipeline(
+    import pilotann_b200
+    # the call of pilot_ann/layers/staged.py:207-227, keyword for keyword
+    call = dict(
         graph=[index.fullgraph.indptr, index.fullgraph.indices], storage=index.storage,
         subgraph=[index.subgraph.indptr, index.subgraph.indices],
         subgraph_cuda=[index.subgraph_cuda.indptr, index.subgraph_cuda.indices,
                        index.mapping_cuda],
         storage_cuda=index.storage_cuda, query=rot.cpu(), query_cuda=red, initial_I=EP_I,
-        initial_D=EP_D, k=10, n_neighbors=32, ef_search=32, d_principle=w.d_principle,
-        chunk_size=64, refine=refine)
-    assert utils.recall(I, utils.ground_truth(q, x, 10)) > 0.90
-    with pytest.raises(RuntimeError):          # pipeline_cpu.cpp:58
-        kernels.pipeline(
-            graph=[index.fullgraph.indptr, index.fullgraph.indices], storage=index.storage,
-            subgraph=[index.subgraph.indptr, index.subgraph.indices],
-            subgraph_cuda=[index.subgraph_cuda.indptr, index.subgraph_cuda.indices,
-                           index.mapping_cuda],
-            storage_cuda=index.storage_cuda, query=rot.cpu(), query_cuda=red, initial_I=EP_I,
-            initial_D=EP_D, k=10, n_neighbors=32, ef_search=32, d_principle=w.d_principle,
-            chunk_size=100, refine=refine)
+        initial_D=EP_D, k=10, n_neighbors=32, ef_search=32, d_principle=w.d_principle)
+    truth = utils.ground_truth(q, x, 10)
+    try:
+        pilotann_b200.set_refine(refine)           # a CPU consumer, overlapped with the GPU
+        I, D = kernels.pipeline(chunk_size=64, **call)
+        assert utils.recall(I, truth) > 0.90
+        with pytest.raises(RuntimeError):          # pipeline_cpu.cpp:58
+            kernels.pipeline(chunk_size=100, **call)
+        pilotann_b200.set_refine(None)
+        with pytest.raises(RuntimeError, match="set_refine"):
+            kernels.pipeline(chunk_size=64, **call)
+    finally:
+        pilotann_b200.set_refine("gpu")
+    # default consumer: the refinement kernel; the same answer as the oracle's
+    # restatement of traverse_refine in that kernel's summation order, fed the same
+    # handoff, bit for bit -- twice (the second call reuses every buffer)
+    hI = torch.empty(q.size(0), 4, 32, dtype=torch.int64, device="cuda")
+    hD = torch.empty(q.size(0), 4, 32, device="cuda")
+    extension.traverse_cuda(hI, hD, index.subgraph_cuda.indptr, index.subgraph_cuda.indices,
+                            index.mapping_cuda, index.storage_cuda, red, EP_I, EP_D, 32)
+    torch.cuda.synchronize()
+    w_I, w_D = oracle_lib.refine_ex(hI.view(q.size(0), -1).cpu(), hD.view(q.size(0), -1).cpu(),
+                                    call["subgraph"], call["graph"], index.storage, rot.cpu(), 10,
+                                    32, w.d_principle, gpu_order=True)
+    for _ in range(2):
+        gI, gD = kernels.pipeline(chunk_size=64, **call)
+        assert gI.device.type == "cpu" and gI.shape == (q.size(0), 10)
+        assert torch.equal(gI, w_I) and torch.equal(gD.view(torch.int32), w_D.view(torch.int32))
+    assert utils.recall(gI, truth) > 0.90
+    # positional order of extension/entry.cpp:48-56
+    pI, pD = extension.pipeline(call["graph"], call["subgraph"], call["subgraph_cuda"],
+                                call["storage"], call["storage_cuda"], call["query"],
+                                call["query_cuda"], EP_I, EP_D, 32, 32, w.d_principle, 10, 128)
+    assert torch.equal(pI, w_I)
+
+
+def test_search_finishes_on_the_gpu_by_default(small_index, oracle_lib):
+    """IndexStaged.search with upstream's signature and nothing else: top-k from
+    the device, equal to the oracle's traverse_refine (kernel summation order) on
+    the stage's own handoff; the stage-2 rows likewise."""
+    from pilotann_b200 import utils
+    index, x, q, w = small_index
+    k, ef = 10, 32
+    I, D = index.search(q, k, ef, 64)
+    assert I.shape == (q.size(0), k) and I.device.type == "cpu"
+    hI, hD, rot = index.search_candidates(q, ef)
+    sub = [index.subgraph.indptr, index.subgraph.indices]
+    full = [index.fullgraph.indptr, index.fullgraph.indices]
+    bI, bD = hI.clone(), hD.clone()
+    w_I, w_D = oracle_lib.refine_ex(bI, bD, sub, full, index.storage, rot.clone(), k, ef,
+                                    w.d_principle, gpu_order=True)
+    assert torch.equal(I, w_I) and torch.equal(D.view(torch.int32), w_D.view(torch.int32))
+    s_I, s_D, _ = index.search_candidates(q, ef, stage2=True)
+    assert torch.equal(s_I, bI) and torch.equal(s_D.view(torch.int32), bD.view(torch.int32))
+    assert utils.recall(I, utils.ground_truth(q, x, k)) > 0.90
+    # device-resident variant
+    dI, dD = index.stage.search_device(q.cuda(), ef, k=k)
+    index.stage.synchronize()
+    assert torch.equal(dI.cpu(), I)
+
+
+def test_submit_wait_slots(small_index):
+    """Chunks in flight on the stage's slots: same rows as the blocking call,
+    pinned buffers that persist, and the state errors."""
+    index, x, q, w = small_index
+    stage = index.stage
+    ef = 32
+    assert stage.slot_rows == 128                      # max_batch 256 over two streams
+    want_I, want_D, want_rot = index.search_candidates(q, ef)
+    stage.submit(0, q[:128].contiguous(), ef, want_rotated=True)
+    stage.submit(1, q[128:256].contiguous(), ef, want_rotated=True)
+    with pytest.raises(RuntimeError, match="still holds"):
+        stage.submit(1, q[:8].contiguous(), ef)
+    a = stage.wait(0)
+    b = stage.wait(1)
+    assert torch.equal(a[0], want_I[:128]) and torch.equal(b[0], want_I[128:])
+    assert torch.equal(a[1], want_D[:128]) and torch.equal(b[2], want_rot[128:])
+    with pytest.raises(RuntimeError, match="holds no chunk"):
+        stage.wait(0)
+    with pytest.raises(RuntimeError):
+        stage.submit(0, torch.zeros(129, w.d_model), ef)
+    addr = a[0].data_ptr()
+    stage.submit(0, q[:64].contiguous(), ef, k=10)     # top-k through the same slot
+    c = stage.wait(0)
+    assert c[0].shape == (64, 10) and c[0].data_ptr() == addr
+    top_I, _ = index.search(q[:64], 10, ef)
+    assert torch.equal(c[0], top_I)
