@@ -94,11 +94,87 @@ def _topk_candidates(x: torch.Tensor, lo: int, hi: int, n_cand: int,
     return torch.cat(ids), torch.cat(dists)
 
 
+class _Cells:
+    """Coarse partition of the vectors for candidate generation at large N: every
+    node belongs to the cell of its nearest of ``n_cells`` sampled vectors, and
+    looks for neighbours only among the members of the ``n_probe`` cells nearest to
+    its own cell's centre -- the scan per node shrinks from N to about
+    ``n_probe * N / n_cells`` vectors.  Members of a cell are kept in ascending id
+    order, so "the members inserted so far" is a prefix of the cell."""
+
+    def __init__(self, x: torch.Tensor, n_cells: int, n_probe: int, seed: int = 0,
+                 chunk: int = 1 << 18):
+        N = x.size(0)
+        dev = x.device
+        g = torch.Generator().manual_seed(seed)
+        pick = torch.randperm(N, generator=g)[:n_cells].to(dev)
+        self.centres = x[pick]
+        c2 = (self.centres * self.centres).sum(-1)
+        cell = torch.empty(N, dtype=torch.long, device=dev)
+        for s in range(0, N, chunk):
+            q = x[s:s + chunk]
+            cell[s:s + chunk] = torch.argmin(c2.unsqueeze(0) - 2.0 * q @ self.centres.T, dim=1)
+        self.n_cells, self.n_probe, self.N = n_cells, min(n_probe, n_cells), N
+        self.order = torch.argsort(cell, stable=True)            # by cell, ids ascending inside
+        self.key = cell[self.order] * N + self.order              # sorted
+        self.probe = torch.topk(_pairwise_sq(self.centres, self.centres), self.n_probe, dim=1,
+                                largest=False).indices            # [n_cells, n_probe], own cell first
+
+    def bounds(self, limit: int) -> torch.Tensor:
+        """Per cell: position in ``order`` of its first member with id >= limit."""
+        cells = torch.arange(self.n_cells, device=self.key.device)
+        return torch.searchsorted(self.key, cells * self.N + limit)
+
+    def candidates(self, x: torch.Tensor, lo: int, hi: int, n_cand: int,
+                   max_block: int = 1 << 28) -> tuple[torch.Tensor, torch.Tensor]:
+        """``n_cand`` nearest nodes among [0, hi), probed cells only, for every node
+        of [lo, hi): ids / distances [hi - lo, n_cand], ``-1`` / ``inf`` padded."""
+        dev = x.device
+        out_i = torch.full((hi - lo, n_cand), -1, dtype=torch.long, device=dev)
+        out_d = torch.full((hi - lo, n_cand), float("inf"), dtype=x.dtype, device=dev)
+        start = self.bounds(0).tolist()
+        from_lo = self.bounds(lo).tolist()
+        to_hi = self.bounds(hi).tolist()
+        probe = self.probe.tolist()
+        for c in range(self.n_cells):
+            if to_hi[c] == from_lo[c]:
+                continue
+            mine = self.order[from_lo[c]:to_hi[c]]                # this cell's nodes in the batch
+            cand = torch.cat([self.order[start[p]:to_hi[p]] for p in probe[c]])
+            if cand.numel() == 0:
+                continue
+            base = x[cand]
+            b2 = (base * base).sum(-1)
+            k = min(n_cand, cand.numel())
+            rows = max(1, max_block // max(1, cand.numel()))
+            for s in range(0, mine.numel(), rows):
+                ids = mine[s:s + rows]
+                q = x[ids]
+                d = (q * q).sum(-1, keepdim=True) + b2.unsqueeze(0) - 2.0 * q @ base.T
+                d[cand.unsqueeze(0) == ids.unsqueeze(1)] = float("inf")
+                dd, ii = torch.topk(d, k, dim=1, largest=False)
+                found = cand[ii]
+                found[torch.isinf(dd)] = -1
+                out_i[ids - lo, :k] = found
+                out_d[ids - lo, :k] = dd.clamp_min_(0.0)
+        return out_i, out_d
+
+
+#: above this many vectors the candidate scans are restricted to nearby cells
+CELL_THRESHOLD = 1_500_000
+
+
 @torch.no_grad()
 def build_graph(x: torch.Tensor, n_neighbors: int, ef_construct: int = 80,
                 first_batch: int = 1024, growth: float = 1.5,
-                chunk_bytes: int = 1 << 30, keep_pruned: bool = False) -> torch.Tensor:
-    """Returns the adjacency as an int64 tensor [N, n_neighbors], ``-1`` padded."""
+                chunk_bytes: int = 1 << 30, keep_pruned: bool = False,
+                cells: "_Cells | None | str" = "auto", exact_below: int = 200_000) -> torch.Tensor:
+    """Returns the adjacency as an int64 tensor [N, n_neighbors], ``-1`` padded.
+
+    ``cells``: ``"auto"`` restricts the candidate scans to nearby cells (see
+    :class:`_Cells`) once N exceeds ``CELL_THRESHOLD``; ``None`` always scans
+    exactly; batches whose scan covers fewer than ``exact_below`` vectors are
+    always exact."""
     assert x.dim() == 2
     N, d = x.shape
     dev = x.device
@@ -108,13 +184,21 @@ def build_graph(x: torch.Tensor, n_neighbors: int, ef_construct: int = 80,
     adj_d = torch.full((N, M), float("inf"), dtype=x.dtype, device=dev)
     if N <= 1:
         return adj
+    if isinstance(cells, str):
+        cells = None
+        if N > CELL_THRESHOLD:
+            n_cells = max(64, int(round((N / 2400) / 64)) * 64)
+            cells = _Cells(x, n_cells=n_cells, n_probe=8)
     # rows of distance matrix / gathered candidate vectors held at once
     prune_rows = max(64, chunk_bytes // (C * max(d, C) * 4 * 3))
     lo = 0
     hi = min(N, first_batch)
     while lo < N:
         scan_rows = max(64, chunk_bytes // (hi * 4 * 3))
-        cand, cand_d = _topk_candidates(x, lo, hi, C, scan_rows)
+        if cells is not None and hi > exact_below:
+            cand, cand_d = cells.candidates(x, lo, hi, C)
+        else:
+            cand, cand_d = _topk_candidates(x, lo, hi, C, scan_rows)
         rev_src, rev_dst, rev_d = [], [], []
         for s in range(0, hi - lo, prune_rows):
             e = min(hi - lo, s + prune_rows)
