@@ -41,6 +41,8 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
     obj_dir = LIB_DIR / "obj"
     obj_dir.mkdir(parents=True, exist_ok=True)
     extra = ["-Xptxas", "-v"] if ptxas_info else []
+    # build parameters of the kernels (e.g. PA_MIN_CTAS=8), space separated NAME=VALUE
+    extra += ["-D" + d for d in os.environ.get("PILOTANN_B200_DEFINES", "").split()]
 
     def compile_one(src: Path) -> tuple[Path, str]:
         obj = obj_dir / (src.stem + ".o")

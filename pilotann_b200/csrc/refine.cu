@@ -12,9 +12,21 @@
 //            with full-dimension distances, up to 2 * ef expansions, top-k out.
 //
 // The candidates are consumed where the traversal left them, in HBM; nothing of
-// the handoff crosses PCIe.  One CTA of four warps per query, persistent: CTA i
+// the handoff crosses PCIe.  One CTA of five warps per query, persistent: CTA i
 // owns slot i of the visited-set pool (visited.cu) and walks the batch with
-// stride gridDim.x.  Semantics are upstream's, operation for operation:
+// stride gridDim.x.  Warp 0 is the heap warp (one thread runs upstream's heap
+// routines), warps 1-4 gather: adjacency row, visited marks, vector rows,
+// distances.  In the full-graph stage the two sides overlap: the node the next
+// pop will return is known as soon as the distances of the current expansion are
+// (it is the better of the open heap's root and the best new neighbour -- a new
+// key below the root always sifts up to the root, equal keys never pass it), so
+// the gather warps start on that node while the heap thread still inserts the
+// current expansion's neighbours and pops.  The pop then either confirms the
+// node or ends the search (when the best new neighbour is not admitted to the
+// heaps the next pop fails the stop test), in which case the speculative marks
+// are never looked at again.  The sub-graph stage does not speculate: its marks
+// are inherited by the full-graph stage.  Semantics are upstream's, operation
+// for operation:
 //   * the result heap (H entries) and the open heap (2H entries) are upstream's
 //     array heaps with upstream's routines (extension/inc/heapq.cuh:13-87) --
 //     heap_replace evicts the leaf reached by walking larger children, not the
@@ -34,10 +46,21 @@
 
 namespace pa {
 
-constexpr int kRefThreads = 128;
+constexpr int kRefThreads = 160;
 constexpr int kRefWarps = kRefThreads / 32;
+constexpr int kGatherWarps = kRefWarps - 1;  // warp 0 runs the heaps
 #ifndef PA_REFINE_MIN_CTAS
 #define PA_REFINE_MIN_CTAS 7
+#endif
+// PA_REFINE_PROFILE=1 (experiments only): thread 0 accumulates clock deltas per
+// phase into stats[b * 16 + 4 ..]; the stats rows are then 16 ints wide.
+#ifndef PA_REFINE_PROFILE
+#define PA_REFINE_PROFILE 0
+#endif
+#if PA_REFINE_PROFILE
+#define PA_TICK(slot) do { if (threadIdx.x == 0) { const long long now__ = clock64(); prof[slot] += static_cast<int>(now__ - prof_t); prof_t = now__; } } while (0)
+#else
+#define PA_TICK(slot) do { } while (0)
 #endif
 constexpr int kMaxDegree = 64;
 constexpr unsigned kAll = 0xffffffffu;
@@ -181,9 +204,72 @@ struct RefShared {
     HeapEntry *buf;    // [H + 2]
     int32_t *c_id;     // [n_cand] seeds of the running stage, then its output
     float *c_d;
-    int32_t *nb_id;    // [kMaxDegree] unvisited neighbours of the expanded node
-    float *nb_d;
+    int32_t *nb_id;    // [2][kMaxDegree] unvisited neighbours of an expanded node
+    float *nb_d;       //                 (two expansions are in flight)
 };
+
+// What the heap thread publishes after a pop, and the gather side's guess.
+struct RefCtl {
+    int pop_u[2];       // node popped for expansion i (slot i & 1), -1: the search ends
+    float root_k[2];    // open heap's root right after that pop
+    int root_v[2];
+    int guess[2];       // node the gather warps prepared expansion i for
+    int n_new[2];       // unvisited neighbours found for expansion i
+    int marker;
+};
+
+__device__ __forceinline__ void gather_sync() {  // the gather warps only
+    asm volatile("bar.sync 1, %0;" ::"n"(32 * kGatherWarps) : "memory");
+}
+
+// The gather half of one expansion (traverse_cpu.cpp:105-135 without the heap
+// updates): the row of u in order up to its first negative id, unvisited ids
+// marked and compacted in row order into buffer p, their full-dimension distances.
+// Called by all gather warps.
+__device__ __forceinline__ void gather_node(const RefineArgs &A, const RefShared &S,
+                                            const RefGraph &G, uint8_t *vis, uint8_t marker,
+                                            RefCtl *ctl, int u, int p, int gw, int lane) {
+    int32_t *nb_id = S.nb_id + p * kMaxDegree;
+    float *nb_d = S.nb_d + p * kMaxDegree;
+    const int d = A.d;
+    if (gw == 0) {
+        const int64_t row = G.row_of != nullptr ? __ldg(G.row_of + u) : u;
+        int count = 0;
+        bool ended = row < 0;
+        for (int c = 0; c < G.degree; c += 32) {
+            const int slot = c + lane;
+            int v = -1;
+            if (!ended && slot < G.degree)
+                v = __ldg(G.nbr + row * G.row_stride + static_cast<int64_t>(slot) * G.elem_stride);
+            const unsigned end_mask = __ballot_sync(kAll, v < 0 && v != kDupTag);
+            const int first_end = end_mask ? __ffs(end_mask) - 1 : 32;
+            const bool live = lane < first_end && v >= 0;
+            bool fresh = false;
+            if (live) {
+                fresh = vis[v] != marker;
+                if (fresh) vis[v] = marker;
+            }
+            const unsigned m = __ballot_sync(kAll, fresh);
+            if (fresh) nb_id[count + __popc(m & ((1u << lane) - 1u))] = v;
+            count += __popc(m);
+            ended = ended || end_mask != 0;
+        }
+        if (lane == 0) ctl->n_new[p] = count;
+    }
+    gather_sync();
+    const int n_new = ctl->n_new[p];
+    for (int j = gw; j < n_new; j += 2 * kGatherWarps) {
+        const int j1 = j + kGatherWarps;
+        const int v0 = nb_id[j], v1 = j1 < n_new ? nb_id[j1] : v0;
+        float r0, r1;
+        two_rows(A.storage + static_cast<int64_t>(v0) * d, A.storage + static_cast<int64_t>(v1) * d,
+                 S.q, d, 0, lane, r0, r1);
+        if (lane == 0) {
+            nb_d[j] = r0;
+            if (j1 < n_new) nb_d[j1] = r1;
+        }
+    }
+}
 
 // One call of upstream's traverse_cpu_kernel: seeds in c_id / c_d (n_seed of
 // them), the result (k_out entries, ascending behind (-1, -inf) pads) back into
@@ -193,9 +279,11 @@ struct RefShared {
 __device__ __forceinline__ void search_stage(const RefineArgs &A, const RefShared &S,
                                              const RefGraph &G, uint8_t *vis, uint8_t marker,
                                              int n_seed, int from, int max_iter, int k_out,
-                                             int *ctl, int &n_expand, int &n_eval) {
+                                             bool speculate, RefCtl *ctl, int &n_expand, int &n_eval, int *prof,
+                                             long long &prof_t) {
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     const int d = A.d, H = A.H;
+    (void)prof; (void)prof_t;
     // distances completed over the trailing dims (:41-62), in place
     if (from < d) {
         for (int i = w; i < n_seed; i += 2 * kRefWarps) {
@@ -220,73 +308,81 @@ __device__ __forceinline__ void search_stage(const RefineArgs &A, const RefShare
         if (id >= 0) vis[id] = marker;
     }
     __syncthreads();
+    PA_TICK(0);
     if (tid == 0) {
         for (int i = 0; i < n_seed; ++i) {
             const int id = S.c_id[i];
             if (id >= 0) heap_replace(S.open, 2 * H, S.c_d[i], id);
         }
     }
-    // :82-136
+    PA_TICK(1);
+    // :82-136.  Expansion i uses slot i & 1 of the control block and of the
+    // neighbour buffers.  Per expansion one CTA-wide barrier: behind it the heap
+    // thread has popped node i (or ended the search) and -- when speculating --
+    // the gather warps have prepared the node they expected.
+    if (tid == 0) {
+        const HeapEntry u = heap_pop(S.open, 2 * H);
+        const bool stop = max_iter <= 0 || u.v < 0 || u.k >= -S.buf[1].k;
+        ctl->pop_u[0] = stop ? -1 : u.v;
+        ctl->root_k[0] = S.open[1].k;
+        ctl->root_v[0] = S.open[1].v;
+        ctl->guess[0] = ctl->guess[1] = -2;
+    }
+    PA_TICK(2);
     for (int step = 0; step < max_iter; ++step) {
-        if (tid == 0) {
-            const HeapEntry u = heap_pop(S.open, 2 * H);
-            const bool stop = u.v < 0 || u.k >= -S.buf[1].k;
-            ctl[0] = stop ? -1 : u.v;
-        }
+        const int p = step & 1;
         __syncthreads();
-        const int u = ctl[0];
+        PA_TICK(4);
+        const int u = ctl->pop_u[p];
         if (u < 0) break;
-        if (w == 0) {
-            // the row of u in order, up to its first negative id; unvisited ids are
-            // marked and compacted in row order (:105-121)
-            const int64_t row = G.row_of != nullptr ? __ldg(G.row_of + u) : u;
-            int count = 0;
-            bool ended = row < 0;
-            for (int c = 0; c < G.degree; c += 32) {
-                const int slot = c + lane;
-                int v = -1;
-                if (!ended && slot < G.degree)
-                    v = __ldg(G.nbr + row * G.row_stride + static_cast<int64_t>(slot) * G.elem_stride);
-                const unsigned end_mask = __ballot_sync(kAll, v < 0 && v != kDupTag);
-                const int first_end = end_mask ? __ffs(end_mask) - 1 : 32;
-                const bool live = lane < first_end && v >= 0;
-                bool fresh = false;
-                if (live) {
-                    fresh = vis[v] != marker;
-                    if (fresh) vis[v] = marker;
-                }
-                const unsigned m = __ballot_sync(kAll, fresh);
-                if (fresh) S.nb_id[count + __popc(m & ((1u << lane) - 1u))] = v;
-                count += __popc(m);
-                ended = ended || end_mask != 0;
-            }
-            if (lane == 0) ctl[1] = count;
+        if (u != ctl->guess[p]) {  // CTA-uniform: nothing, or something else, was prepared
+            if (w > 0) gather_node(A, S, G, vis, marker, ctl, u, p, w - 1, lane);
+            __syncthreads();
         }
-        __syncthreads();
-        const int n_new = ctl[1];
-        // full-dimension distances of the unvisited neighbours (:123-135)
-        for (int j = w; j < n_new; j += 2 * kRefWarps) {
-            const int j1 = j + kRefWarps;
-            const int v0 = S.nb_id[j], v1 = j1 < n_new ? S.nb_id[j1] : v0;
-            float r0, r1;
-            two_rows(A.storage + static_cast<int64_t>(v0) * d,
-                     A.storage + static_cast<int64_t>(v1) * d, S.q, d, 0, lane, r0, r1);
-            if (lane == 0) {
-                S.nb_d[j] = r0;
-                if (j1 < n_new) S.nb_d[j1] = r1;
-            }
-        }
-        __syncthreads();
-        if (tid == 0) {  // heap_update (:23-39), row order
+        PA_TICK(3);
+        if (tid == 0) {
+            // heap_update (:23-39) in row order, then the next pop (:84-90)
+            const int n_new = ctl->n_new[p];
+            const int32_t *nb_id = S.nb_id + p * kMaxDegree;
+            const float *nb_d = S.nb_d + p * kMaxDegree;
             ++n_expand;
             n_eval += n_new;
             for (int j = 0; j < n_new; ++j) {
-                const float dist = S.nb_d[j];
+                const float dist = nb_d[j];
                 if (dist >= -S.buf[1].k) continue;
-                heap_pushpop(S.buf, H, -dist, S.nb_id[j]);
-                heap_replace(S.open, 2 * H, dist, S.nb_id[j]);
+                heap_pushpop(S.buf, H, -dist, nb_id[j]);
+                heap_replace(S.open, 2 * H, dist, nb_id[j]);
             }
+            if (step + 1 < max_iter) {
+                const HeapEntry nx = heap_pop(S.open, 2 * H);
+                const bool stop = nx.v < 0 || nx.k >= -S.buf[1].k;
+                ctl->pop_u[p ^ 1] = stop ? -1 : nx.v;
+                ctl->root_k[p ^ 1] = S.open[1].k;
+                ctl->root_v[p ^ 1] = S.open[1].v;
+            }
+        } else if (w > 0 && speculate && step + 1 < max_iter) {
+            // the node the next pop returns unless it ends the search: the first
+            // new neighbour with the smallest distance if that is below the root
+            // the open heap had after this expansion's pop, else that root
+            const int n_new = ctl->n_new[p];
+            const float *nb_d = S.nb_d + p * kMaxDegree;
+            float best = CUDART_INF_F;
+            int at = 0x7fffffff;
+            for (int j = lane; j < n_new; j += 32) {
+                const float dist = nb_d[j];
+                if (dist < best) { best = dist; at = j; }
+            }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) {
+                const float ob = __shfl_xor_sync(kAll, best, off);
+                const int oa = __shfl_xor_sync(kAll, at, off);
+                if (ob < best || (ob == best && oa < at)) { best = ob; at = oa; }
+            }
+            const int guess = best < ctl->root_k[p] ? S.nb_id[p * kMaxDegree + at] : ctl->root_v[p];
+            if (tid == 32) ctl->guess[p ^ 1] = guess;
+            if (guess >= 0) gather_node(A, S, G, vis, marker, ctl, guess, p ^ 1, w - 1, lane);
         }
+        PA_TICK(5);
     }
     // :139-162: the seeds join the result heap; all but k_out are dropped; what is
     // left comes out worst first and is stored ascending
@@ -312,11 +408,13 @@ __device__ __forceinline__ void search_stage(const RefineArgs &A, const RefShare
         S.c_d[i] = -CUDART_INF_F;
     }
     __syncthreads();
+    PA_TICK(6);
 }
 
 __global__ void __launch_bounds__(kRefThreads, PA_REFINE_MIN_CTAS) refine_kernel(RefineArgs A) {
     extern __shared__ __align__(16) unsigned char ref_smem[];
-    __shared__ int ctl[4];
+    __shared__ RefCtl ctl_s;
+    RefCtl *ctl = &ctl_s;
     RefShared S;
     S.q = reinterpret_cast<float *>(ref_smem);
     S.open = reinterpret_cast<HeapEntry *>(S.q + A.d);
@@ -324,7 +422,7 @@ __global__ void __launch_bounds__(kRefThreads, PA_REFINE_MIN_CTAS) refine_kernel
     S.c_id = reinterpret_cast<int32_t *>(S.buf + A.H + 2);
     S.c_d = reinterpret_cast<float *>(S.c_id + A.n_cand);
     S.nb_id = reinterpret_cast<int32_t *>(S.c_d + A.n_cand);
-    S.nb_d = reinterpret_cast<float *>(S.nb_id + kMaxDegree);
+    S.nb_d = reinterpret_cast<float *>(S.nb_id + 2 * kMaxDegree);
     const int tid = threadIdx.x;
     const int slot = A.slot_begin + blockIdx.x;
     uint8_t *vis = A.marks + static_cast<int64_t>(slot) * A.slot_stride;
@@ -332,9 +430,9 @@ __global__ void __launch_bounds__(kRefThreads, PA_REFINE_MIN_CTAS) refine_kernel
     for (int64_t b = blockIdx.x; b < A.batch; b += gridDim.x) {
         // next marker of this slot; the array is wiped when the markers run out
         // (bitmask.hpp:17-36 does the same on wrap-around)
-        if (tid == 0) ctl[2] = A.epoch[slot] + 1;
+        if (tid == 0) ctl->marker = A.epoch[slot] + 1;
         __syncthreads();
-        int marker = ctl[2];
+        int marker = ctl->marker;
         if (marker > 254) {
             uint4 *p = reinterpret_cast<uint4 *>(vis);
             for (int64_t i = tid; i < A.slot_stride / 16; i += kRefThreads)
@@ -352,13 +450,15 @@ __global__ void __launch_bounds__(kRefThreads, PA_REFINE_MIN_CTAS) refine_kernel
         }
         __syncthreads();
         int st[4] = {0, 0, 0, 0};
+        int prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        long long prof_t = clock64();
         // stage 2 (traverse_cpu.cpp:317-326): sub-graph, REFINE_STEP expansions
         search_stage(A, S, A.sub, vis, static_cast<uint8_t>(marker), A.n_cand, A.d_p,
-                     min(2, 2 * A.ef), A.n_cand, ctl, st[0], st[1]);
+                     min(2, 2 * A.ef), A.n_cand, false, ctl, st[0], st[1], prof, prof_t);
         int k_out = A.n_cand;
         if (A.stages >= 3) {  // stage 3 (:327-336): full graph, same marker
             search_stage(A, S, A.full, vis, static_cast<uint8_t>(marker), A.n_cand, A.d,
-                         min(1024, 2 * A.ef), A.k, ctl, st[2], st[3]);
+                         min(1024, 2 * A.ef), A.k, true, ctl, st[2], st[3], prof, prof_t);
             k_out = A.k;
         }
         for (int i = tid; i < k_out; i += kRefThreads) {
@@ -366,8 +466,13 @@ __global__ void __launch_bounds__(kRefThreads, PA_REFINE_MIN_CTAS) refine_kernel
             A.out_D[b * k_out + i] = S.c_d[i];
         }
         if (A.stats != nullptr && tid == 0) {
+#if PA_REFINE_PROFILE
+            for (int i = 0; i < 4; ++i) A.stats[b * 16 + i] = st[i];
+            for (int i = 0; i < 8; ++i) A.stats[b * 16 + 4 + i] = prof[i];
+#else
 #pragma unroll
             for (int i = 0; i < 4; ++i) A.stats[b * 4 + i] = st[i];
+#endif
         }
         __syncthreads();
     }
@@ -383,7 +488,7 @@ static int cpu_heap_size_for(int ef) {
 
 static size_t refine_smem_bytes(int d, int H, int n_cand) {
     return sizeof(float) * d + sizeof(HeapEntry) * (3 * H + 4) + 8 * static_cast<size_t>(n_cand) +
-           8 * kMaxDegree;
+           16 * kMaxDegree;
 }
 
 static int refine_launch(const RefineArgs &A, int n_slots, cudaStream_t stream) {

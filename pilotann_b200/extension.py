@@ -323,8 +323,8 @@ class VisitedPool:
         return int(_C.lib().pa_visited_pool_bytes(n_nodes, n_slots))
 
     def close(self) -> None:
-        if getattr(self, "_h", None):
-            _C.lib().pa_visited_pool_destroy(self._h)
+        if getattr(self, "_h", None) and _C is not None and _C.lib is not None:
+            _C.lib().pa_visited_pool_destroy(self._h)   # (module globals are gone at exit)
             self._h = None
 
     __del__ = close

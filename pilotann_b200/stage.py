@@ -88,8 +88,8 @@ class SearchStage:
         return _C.PA_OUT_STAGE2 if stage2 else _C.PA_OUT_HANDOFF
 
     def close(self) -> None:
-        if getattr(self, "_h", None):
-            _C.lib().pa_stage_destroy(self._h)
+        if getattr(self, "_h", None) and _C is not None and _C.lib is not None:
+            _C.lib().pa_stage_destroy(self._h)       # (module globals are gone at exit)
             self._h = None
 
     __del__ = close
