@@ -46,7 +46,7 @@ TARGET_RECALL = 0.90
 # ef_search at which GPU stage + upstream CPU refinement reach recall@10 >= 0.90 on
 # the seeded workloads (re-measured by the CPU leg of every N=1 run, which reports
 # the recall it sees at this ef)
-OPERATING_EF = {1: 32, 2: 128, 3: 128}
+OPERATING_EF = {2: 128}
 # ncu dram__bytes_read.sum + dram__bytes_write.sum per traversal launch divided by
 # the queries in that launch (bytes / query), stamped with the state of the kernel
 # it was captured on; None until captured
