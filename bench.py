@@ -50,8 +50,11 @@ OPERATING_EF = {2: 128}
 # ncu dram__bytes_read.sum + dram__bytes_write.sum per traversal launch divided by
 # the queries in that launch (bytes / query), stamped with the state of the kernel
 # it was captured on; None until captured
-NCU_TRAFFIC_PER_QUERY = {2: {"bytes_per_query": 1.497034e9 / 1024,
-                             "captured_at": "commit 49677c7, library version 101"}}
+NCU_TRAFFIC_PER_QUERY = {2: {
+    "traverse": {"bytes_per_query": (1.489819e9 + 7.637e6) / 1024,
+                 "captured_at": "library version 102, 1024 queries, ef 128"},
+    "refine": {"bytes_per_query": (11.399857e9 + 0.135339e9) / 1024,
+               "captured_at": "library version 102, 1024 queries, ef 128"}}}
 PASSES = 10       # event-timed passes per step; a step's time is their median
 FALLBACK_HBM_GBS = 6650.0
 
@@ -473,6 +476,48 @@ def refine_parity_leg(w, index, rot, hand_I, hand_D, top_I, top_D, r_stats, ef):
 
 # ---------------------------------------------------------------------- main
 
+def kernel_only(which, w, index, queries, device, ef):
+    """One kernel alone on the workload's index and queries, with only the device
+    memory that kernel needs: the process a profiler capture runs."""
+    from pilotann_b200 import extension
+    B, k = min(w.n_queries, 1024), w.top_k
+    index.to(device, max_batch=B, max_ef=256, refine=None)
+    q = queries[:B].contiguous().to(device)
+    oI, oD = index.stage.search_device(q, ef)
+    index.stage.synchronize()
+    rot = extension.project(q, index.VT_cuda)
+    red = rot[:, :w.d_principle].contiguous()
+    EP_I, EP_D = index.entry.search(red)
+    if which == "refine":
+        storage = index.storage.to(device)
+        full_nbr = extension.pack_fullgraph(index.fullgraph.indptr.to(device),
+                                            index.fullgraph.indices.to(device), index.n_neighbors)
+        pool = extension.VisitedPool(storage.size(0), min(B, 1036), device)
+        tI = torch.empty(B, k, dtype=torch.int64, device=device)
+        tD = torch.empty(B, k, dtype=torch.float32, device=device)
+        call = lambda: extension.refine(oI, oD, rot, storage, index.packed_nbr, index.row_of,
+                                        full_nbr, pool, ef, w.d_principle, k=k, out=(tI, tD))
+    else:
+        call = lambda: extension.traverse_packed(oI, oD, index.packed_nbr, index.row_of,
+                                                 index.storage_cuda, red, EP_I, EP_D,
+                                                 index.n_neighbors)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    times = []
+    for _ in range(4):
+        flush.zero_()
+        torch.cuda.synchronize(device)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        call()
+        b.record()
+        torch.cuda.synchronize(device)
+        times.append(a.elapsed_time(b))
+    emit({"kernel": which, "workload": w.name, "queries": B, "ef_search": ef,
+          "ms": [round(t, 4) for t in times],
+          "device_memory_MB": round(torch.cuda.memory_allocated(device) / 2 ** 20)})
+    return 0
+
+
 def flush_l2(buf):
     buf.zero_()
 
@@ -485,6 +530,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--ef", type=int, default=0, help="override the operating ef_search")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--kernel", default="", choices=["", "traverse", "refine"],
+                    help="run only this kernel a few times on the workload (small process for "
+                         "profiler captures); prints its CUDA-event time")
     args = ap.parse_args()
     steps, warmup = args.steps, max(args.warmup, 3)
 
@@ -537,6 +585,8 @@ def main():
         return 0
 
     from pilotann_b200 import extension
+    if args.kernel:
+        return kernel_only(args.kernel, w, index, queries, device, ef or 128)
     n_probe = min(1024, queries.size(0))
     index.to(device, max_batch=max(B, n_probe), max_ef=max(EF_SWEEP), refine="gpu")
     stage = index.stage
@@ -709,7 +759,8 @@ def main():
             pass
     achieved = algo_bytes / (trav_ms * 1e-3) / 1e9
     ref_achieved = ref_bytes / (ref_ms * 1e-3) / 1e9
-    traffic = NCU_TRAFFIC_PER_QUERY.get(cfg)
+    traffic = NCU_TRAFFIC_PER_QUERY.get(cfg, {}).get("traverse") if ef == 128 else None
+    ref_traffic = NCU_TRAFFIC_PER_QUERY.get(cfg, {}).get("refine") if ef == 128 else None
 
     # ---- max over ranks ----
     times = torch.tensor([total_ms, e2e_s * 1e3, sum(stage_step_ms), e2e_chunked_s * 1e3,
@@ -736,7 +787,9 @@ def main():
             "expansions_per_query": E / B, "evaluations_per_query": C / B}
     refn = {"bound": "hbm", "achieved": ref_achieved, "peak": peak, "unit": "GB/s",
             "frac": ref_achieved / peak, "peak_source": peak_src,
-            "traffic": None, "kernel": "refine_kernel", "kernel_ms": ref_ms,
+            "traffic": None if ref_traffic is None else ref_traffic["bytes_per_query"] * B,
+            "traffic_captured_at": None if ref_traffic is None else ref_traffic["captured_at"],
+            "kernel": "refine_kernel", "kernel_ms": ref_ms,
             "algorithmic_bytes_per_launch": ref_bytes, "candidates_per_query": n_cand / B,
             "stage2_expansions_per_query": float(rs[:, 0].sum()) / B,
             "stage2_evaluations_per_query": float(rs[:, 1].sum()) / B,
