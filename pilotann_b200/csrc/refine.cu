@@ -198,6 +198,28 @@ __device__ __forceinline__ void two_rows(const float *__restrict__ r0, const flo
     o1 = butterfly(a1);
 }
 
+// A third row rides along without registers: cp.async copies it into the warp's
+// own staging buffer while the two register rows make their round trips; every
+// lane later reads back exactly the 16-byte pieces it copied itself.
+__device__ __forceinline__ void row_to_stage(float *stage, const float *__restrict__ row, int d,
+                                             int from, int lane) {
+    for (int o = from + 4 * lane; o < d; o += 128) {
+        const unsigned dst = static_cast<unsigned>(__cvta_generic_to_shared(stage + o));
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(row + o) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+
+__device__ __forceinline__ float staged_row(const float *stage, const float *q_s, int d, int from,
+                                            int lane) {
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    float a = 0.0f;
+    for (int o = from + 4 * lane; o < d; o += 128)
+        a = ref_stripe(a, *reinterpret_cast<const float4 *>(q_s + o),
+                       *reinterpret_cast<const float4 *>(stage + o));
+    return butterfly(a);
+}
+
 struct RefShared {
     float *q;          // [d]
     HeapEntry *open;   // [2H + 2]
@@ -206,6 +228,7 @@ struct RefShared {
     float *c_d;
     int32_t *nb_id;    // [2][kMaxDegree] unvisited neighbours of an expanded node
     float *nb_d;       //                 (two expansions are in flight)
+    float *stage;      // [kRefWarps][d] one staged vector row per warp
 };
 
 // What the heap thread publishes after a pop, and the gather side's guess.
@@ -258,15 +281,21 @@ __device__ __forceinline__ void gather_node(const RefineArgs &A, const RefShared
     }
     gather_sync();
     const int n_new = ctl->n_new[p];
-    for (int j = gw; j < n_new; j += 2 * kGatherWarps) {
-        const int j1 = j + kGatherWarps;
+    // three rows per warp and trip: two through registers, one staged by cp.async
+    float *stage = S.stage + (gw + 1) * d;
+    for (int j = gw; j < n_new; j += 3 * kGatherWarps) {
+        const int j1 = j + kGatherWarps, j2 = j + 2 * kGatherWarps;
         const int v0 = nb_id[j], v1 = j1 < n_new ? nb_id[j1] : v0;
+        if (j2 < n_new) row_to_stage(stage, A.storage + static_cast<int64_t>(nb_id[j2]) * d, d, 0, lane);
         float r0, r1;
         two_rows(A.storage + static_cast<int64_t>(v0) * d, A.storage + static_cast<int64_t>(v1) * d,
                  S.q, d, 0, lane, r0, r1);
+        float r2 = 0.0f;
+        if (j2 < n_new) r2 = staged_row(stage, S.q, d, 0, lane);
         if (lane == 0) {
             nb_d[j] = r0;
             if (j1 < n_new) nb_d[j1] = r1;
+            if (j2 < n_new) nb_d[j2] = r2;
         }
     }
 }
@@ -286,16 +315,22 @@ __device__ __forceinline__ void search_stage(const RefineArgs &A, const RefShare
     (void)prof; (void)prof_t;
     // distances completed over the trailing dims (:41-62), in place
     if (from < d) {
-        for (int i = w; i < n_seed; i += 2 * kRefWarps) {
-            const int i1 = i + kRefWarps;
+        float *stage = S.stage + w * d;
+        for (int i = w; i < n_seed; i += 3 * kRefWarps) {
+            const int i1 = i + kRefWarps, i2 = i + 2 * kRefWarps;
             const int id0 = S.c_id[i], id1 = i1 < n_seed ? S.c_id[i1] : -1;
-            if (id0 < 0 && id1 < 0) continue;  // warp-uniform
+            const int id2 = i2 < n_seed ? S.c_id[i2] : -1;
+            if (id0 < 0 && id1 < 0 && id2 < 0) continue;  // warp-uniform
+            if (id2 >= 0) row_to_stage(stage, A.storage + static_cast<int64_t>(id2) * d, d, from, lane);
             float r0, r1;
             two_rows(A.storage + static_cast<int64_t>(max(id0, 0)) * d,
                      A.storage + static_cast<int64_t>(max(id1, 0)) * d, S.q, d, from, lane, r0, r1);
+            float r2 = 0.0f;
+            if (id2 >= 0) r2 = staged_row(stage, S.q, d, from, lane);
             if (lane == 0) {
                 if (id0 >= 0) S.c_d[i] = __fadd_rn(S.c_d[i], r0);
                 if (id1 >= 0) S.c_d[i1] = __fadd_rn(S.c_d[i1], r1);
+                if (id2 >= 0) S.c_d[i2] = __fadd_rn(S.c_d[i2], r2);
             }
         }
     }
@@ -423,6 +458,7 @@ __global__ void __launch_bounds__(kRefThreads, PA_REFINE_MIN_CTAS) refine_kernel
     S.c_d = reinterpret_cast<float *>(S.c_id + A.n_cand);
     S.nb_id = reinterpret_cast<int32_t *>(S.c_d + A.n_cand);
     S.nb_d = reinterpret_cast<float *>(S.nb_id + 2 * kMaxDegree);
+    S.stage = S.nb_d + 2 * kMaxDegree;
     const int tid = threadIdx.x;
     const int slot = A.slot_begin + blockIdx.x;
     uint8_t *vis = A.marks + static_cast<int64_t>(slot) * A.slot_stride;
@@ -487,8 +523,8 @@ static int cpu_heap_size_for(int ef) {
 }
 
 static size_t refine_smem_bytes(int d, int H, int n_cand) {
-    return sizeof(float) * d + sizeof(HeapEntry) * (3 * H + 4) + 8 * static_cast<size_t>(n_cand) +
-           16 * kMaxDegree;
+    return sizeof(float) * d * (1 + kRefWarps) + sizeof(HeapEntry) * (3 * H + 4) +
+           8 * static_cast<size_t>(n_cand) + 16 * kMaxDegree;
 }
 
 static int refine_launch(const RefineArgs &A, int n_slots, cudaStream_t stream) {
