@@ -99,24 +99,31 @@ struct __align__(8) HeapEntry {
 };
 
 // h[1 .. n] is the heap (upstream index c lives at c + 1); h[n + 1] exists and is
-// never meaningful: the pair load of the last parent may touch it.
-__device__ __forceinline__ void pair_at(const HeapEntry *h, int child, HeapEntry &l, HeapEntry &r) {
-    const int4 p = *reinterpret_cast<const int4 *>(h + child);  // child is even: 16-byte aligned
-    l.k = __int_as_float(p.x); l.v = p.y;
-    r.k = __int_as_float(p.z); r.v = p.w;
+// never meaningful: the pair load of the last parent may touch it.  Both children
+// of node c sit in one aligned 16-byte pair at h + 2c.
+// Both walks below go down one level per step and know the children of the node
+// they stand on; the loads for the NEXT level are issued for both children before
+// the comparison that picks one of them, so a level costs one compare-and-select
+// instead of a shared-memory round trip.  A pair index past the heap is clamped
+// (the pair is then never looked at).
+__device__ __forceinline__ int4 raw_pair(const HeapEntry *h, int child, int n) {
+    return *reinterpret_cast<const int4 *>(h + min(child, n & ~1));
 }
 
 // heapq.cuh:13-29: the root sinks while a child is strictly smaller.
 __device__ __forceinline__ void heap_sink(HeapEntry *h, int n, HeapEntry me) {
-    int cur = 1;
-    for (int child = 2; child <= n; child = 2 * cur) {
-        HeapEntry l, r;
-        pair_at(h, child, l, r);
-        const bool right = (child + 1 <= n) && (r.k < l.k);
-        const HeapEntry c = right ? r : l;
-        if (me.k <= c.k) break;
-        h[cur] = c;
+    int cur = 1, child = 2;
+    int4 p = raw_pair(h, 2, n);
+    while (child <= n) {
+        const int4 pl = raw_pair(h, 2 * child, n), pr = raw_pair(h, 2 * child + 2, n);
+        const float lk = __int_as_float(p.x), rk = __int_as_float(p.z);
+        const bool right = (child + 1 <= n) && (rk < lk);
+        const float ck = right ? rk : lk;
+        if (me.k <= ck) break;
+        h[cur] = HeapEntry{ck, right ? p.w : p.y};
         cur = child + (right ? 1 : 0);
+        child = 2 * cur;
+        p = right ? pr : pl;
     }
     h[cur] = me;
 }
@@ -136,14 +143,17 @@ __device__ __forceinline__ void heap_pushpop(HeapEntry *h, int n, float k, int32
 
 // heapq.cuh:47-77
 __device__ __forceinline__ void heap_replace(HeapEntry *h, int n, float k, int32_t v) {
-    int cur = 1;
+    int cur = 1, child = 2;
     float cur_k = h[1].k;
-    for (int child = 2; child <= n; child = 2 * cur) {
-        HeapEntry l, r;
-        pair_at(h, child, l, r);
-        const bool right = (child + 1 <= n) && (r.k > l.k);
+    int4 p = raw_pair(h, 2, n);
+    while (child <= n) {
+        const int4 pl = raw_pair(h, 2 * child, n), pr = raw_pair(h, 2 * child + 2, n);
+        const float lk = __int_as_float(p.x), rk = __int_as_float(p.z);
+        const bool right = (child + 1 <= n) && (rk > lk);
         cur = child + (right ? 1 : 0);
-        cur_k = right ? r.k : l.k;
+        cur_k = right ? rk : lk;
+        child = 2 * cur;
+        p = right ? pr : pl;
     }
     if (k >= cur_k) return;
     while (cur > 1) {
