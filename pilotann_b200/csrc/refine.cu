@@ -14,8 +14,8 @@
 // The candidates are consumed where the traversal left them, in HBM; nothing of
 // the handoff crosses PCIe.  One CTA of five warps per query, persistent: CTA i
 // owns slot i of the visited-set pool (visited.cu) and walks the batch with
-// stride gridDim.x.  Warp 0 is the heap warp (one thread runs upstream's heap
-// routines), warps 1-4 gather: adjacency row, visited marks, vector rows,
+// stride gridDim.x.  Warp 0 is the heap warp (it runs upstream's heap routines),
+// warps 1-4 gather: adjacency row, visited marks, vector rows,
 // distances.  In the full-graph stage the two sides overlap: the node the next
 // pop will return is known as soon as the distances of the current expansion are
 // (it is the better of the open heap's root and the best new neighbour -- a new
@@ -32,7 +32,8 @@
 //     heap_replace evicts the leaf reached by walking larger children, not the
 //     maximum, so the layout is part of the result; they live in shared memory,
 //     stored 1-based as {key, id} pairs so that both children of a node come in
-//     one 16-byte load, and are driven by one thread;
+//     one 16-byte load, and are driven by the 32 lanes of the heap warp together
+//     (see the routines below);
 //   * H follows upstream's CPU dispatch (traverse_cpu.cpp:228-254);
 //   * exact visited marks (extension/inc/bitmask.hpp:12-45) shared by the two
 //     stages of a query, as upstream shares one marker between them;
@@ -92,7 +93,7 @@ struct RefineArgs {
     int32_t *stats;         // nullptr or [batch, 4]
 };
 
-// ---- upstream's heaps, 1-based {key, id} pairs, one thread -------------------
+// ---- upstream's heaps, 1-based {key, id} pairs, one warp ------------------------
 struct __align__(8) HeapEntry {
     float k;
     int32_t v;
@@ -101,68 +102,115 @@ struct __align__(8) HeapEntry {
 // h[1 .. n] is the heap (upstream index c lives at c + 1); h[n + 1] exists and is
 // never meaningful: the pair load of the last parent may touch it.  Both children
 // of node c sit in one aligned 16-byte pair at h + 2c.
-// Both walks below go down one level per step and know the children of the node
-// they stand on; the loads for the NEXT level are issued for both children before
-// the comparison that picks one of them, so a level costs one compare-and-select
-// instead of a shared-memory round trip.  A pair index past the heap is clamped
-// (the pair is then never looked at).
-__device__ __forceinline__ int4 raw_pair(const HeapEntry *h, int child, int n) {
-    return *reinterpret_cast<const int4 *>(h + min(child, n & ~1));
+//
+// Upstream's routines walk from the root to a leaf, one dependent comparison per
+// level.  Here the 32 lanes of the heap warp look at the five levels below the
+// current node at once: lane l owns the l-th node of that sub-tree (heap order),
+// compares its two children, a ballot collects the 31 decisions, every lane then
+// tests with one mask compare whether its own node lies on the path those
+// decisions describe, and a second ballot yields the path -- its highest set bit
+// is the node five levels down.  Two such steps cover a heap of 1024 entries.  The
+// keys along the path are then loaded one per lane and a ballot tells how far the
+// moving key travels; the shift of the path is one store per lane.  The heap is
+// not touched between the decisions and the stores, so the result is upstream's
+// array, entry for entry (checked on the host against the oracle's routines over
+// 2 M random operations at sizes 1 .. 4096, odd sizes included).
+
+struct WalkLane {    // what a lane needs to know about its place in a 5-level sub-tree
+    int depth, off;  // node = (root << depth) + off
+    unsigned care, want;  // on the path iff (decisions & care) == want
+};
+
+__device__ __forceinline__ WalkLane walk_lane(int lane) {
+    WalkLane L;
+    const int r = lane + 1;
+    L.depth = 31 - __clz(r);
+    L.off = r - (1 << L.depth);
+    L.care = L.want = 0;
+#pragma unroll
+    for (int t = 1; t <= 4; ++t) {
+        if (t <= L.depth) {
+            const int q = r >> t;  // ancestor; it has to point at (r >> (t - 1))
+            L.care |= 1u << (q - 1);
+            L.want |= static_cast<unsigned>((r >> (t - 1)) & 1) << (q - 1);
+        }
+    }
+    return L;
 }
 
-// heapq.cuh:13-29: the root sinks while a child is strictly smaller.
-__device__ __forceinline__ void heap_sink(HeapEntry *h, int n, HeapEntry me) {
-    int cur = 1, child = 2;
-    int4 p = raw_pair(h, 2, n);
-    while (child <= n) {
-        const int4 pl = raw_pair(h, 2 * child, n), pr = raw_pair(h, 2 * child + 2, n);
-        const float lk = __int_as_float(p.x), rk = __int_as_float(p.z);
-        const bool right = (child + 1 <= n) && (rk < lk);
-        const float ck = right ? rk : lk;
-        if (me.k <= ck) break;
-        h[cur] = HeapEntry{ck, right ? p.w : p.y};
-        cur = child + (right ? 1 : 0);
-        child = 2 * cur;
-        p = right ? pr : pl;
+// Leaf reached from the root by taking the larger (kLarger) or the smaller child
+// at every node; the right child wins only if it exists and is strictly larger /
+// smaller (heapq.cuh:17-21, 53-57).
+template <bool kLarger>
+__device__ __forceinline__ int warp_walk(const HeapEntry *h, int n, int lane, const WalkLane &L) {
+    int a = 1;
+    while (2 * a <= n) {
+        const int node = (a << L.depth) + L.off;
+        const bool valid = lane < 31 && node <= n;
+        const bool has_child = valid && 2 * node <= n;
+        bool right = false;
+        if (has_child) {
+            const int4 p = *reinterpret_cast<const int4 *>(h + 2 * node);
+            const float lk = __int_as_float(p.x), rk = __int_as_float(p.z);
+            right = (2 * node + 1 <= n) && (kLarger ? rk > lk : rk < lk);
+        }
+        const unsigned B = __ballot_sync(kAll, right);
+        const unsigned HC = __ballot_sync(kAll, has_child);
+        const unsigned P = __ballot_sync(kAll, valid && (B & L.care) == L.want);
+        const int rs = 32 - __clz(P);  // deepest node of the path inside the sub-tree (P has bit 0)
+        const int ds = 31 - __clz(rs);
+        const int ns = (a << ds) + (rs - (1 << ds));
+        a = ((HC >> (rs - 1)) & 1u) ? 2 * ns + static_cast<int>((B >> (rs - 1)) & 1u) : ns;
     }
-    h[cur] = me;
+    return a;
+}
+
+// heapq.cuh:13-29: the root sinks while a child is strictly smaller.  `me` takes
+// the root's place first (callers have read the root if they need it).
+__device__ __forceinline__ void warp_sink(HeapEntry *h, int n, HeapEntry me, int lane,
+                                          const WalkLane &L) {
+    const int leaf = warp_walk<false>(h, n, lane, L);
+    const int D = 31 - __clz(leaf);       // path nodes below the root
+    const bool on = lane < D;
+    const int node = on ? leaf >> (D - 1 - lane) : 1;   // lane l: the path node at depth l + 1
+    const HeapEntry e = h[node];
+    const unsigned m = __ballot_sync(kAll, on && e.k < me.k);
+    const int cnt = __ffs(~m) - 1;        // children that move up one level
+    if (lane < cnt) h[node >> 1] = e;
+    if (lane == 0) h[cnt == 0 ? 1 : leaf >> (D - cnt)] = me;
+    __syncwarp();
 }
 
 // heapq.cuh:38-45
-__device__ __forceinline__ HeapEntry heap_pop(HeapEntry *h, int n) {
+__device__ __forceinline__ HeapEntry warp_pop(HeapEntry *h, int n, int lane, const WalkLane &L) {
     const HeapEntry out = h[1];
-    heap_sink(h, n, HeapEntry{CUDART_INF_F, -1});
+    __syncwarp();
+    warp_sink(h, n, HeapEntry{CUDART_INF_F, -1}, lane, L);
     return out;
 }
 
 // heapq.cuh:79-87
-__device__ __forceinline__ void heap_pushpop(HeapEntry *h, int n, float k, int32_t v) {
+__device__ __forceinline__ void warp_pushpop(HeapEntry *h, int n, float k, int32_t v, int lane,
+                                             const WalkLane &L) {
     if (k <= h[1].k) return;
-    heap_sink(h, n, HeapEntry{k, v});
+    __syncwarp();
+    warp_sink(h, n, HeapEntry{k, v}, lane, L);
 }
 
-// heapq.cuh:47-77
-__device__ __forceinline__ void heap_replace(HeapEntry *h, int n, float k, int32_t v) {
-    int cur = 1, child = 2;
-    float cur_k = h[1].k;
-    int4 p = raw_pair(h, 2, n);
-    while (child <= n) {
-        const int4 pl = raw_pair(h, 2 * child, n), pr = raw_pair(h, 2 * child + 2, n);
-        const float lk = __int_as_float(p.x), rk = __int_as_float(p.z);
-        const bool right = (child + 1 <= n) && (rk > lk);
-        cur = child + (right ? 1 : 0);
-        cur_k = right ? rk : lk;
-        child = 2 * cur;
-        p = right ? pr : pl;
-    }
-    if (k >= cur_k) return;
-    while (cur > 1) {
-        const HeapEntry parent = h[cur >> 1];
-        if (parent.k <= k) break;
-        h[cur] = parent;
-        cur >>= 1;
-    }
-    h[cur] = HeapEntry{k, v};
+// heapq.cuh:47-77: the leaf at the end of the larger-child walk is replaced if the
+// new key is smaller, then sifted up while the parent is strictly larger.
+__device__ __forceinline__ void warp_replace(HeapEntry *h, int n, float k, int32_t v, int lane,
+                                             const WalkLane &L) {
+    const int leaf = warp_walk<true>(h, n, lane, L);
+    if (k >= h[leaf].k) return;
+    const int D = 31 - __clz(leaf);
+    const bool on = lane < D;
+    const HeapEntry e = h[on ? leaf >> (lane + 1) : 1];  // lane l: the ancestor l + 1 levels up
+    const unsigned m = __ballot_sync(kAll, on && e.k > k);
+    const int cnt = __ffs(~m) - 1;        // ancestors that move down one level
+    if (lane < cnt) h[leaf >> lane] = e;
+    if (lane == 0) h[leaf >> cnt] = HeapEntry{k, v};
+    __syncwarp();
 }
 
 // ---- distances: one warp per row, two rows in flight ----------------------------
@@ -354,10 +402,11 @@ __device__ __forceinline__ void search_stage(const RefineArgs &A, const RefShare
     }
     __syncthreads();
     PA_TICK(0);
-    if (tid == 0) {
+    const WalkLane WL = walk_lane(lane);
+    if (w == 0) {
         for (int i = 0; i < n_seed; ++i) {
             const int id = S.c_id[i];
-            if (id >= 0) heap_replace(S.open, 2 * H, S.c_d[i], id);
+            if (id >= 0) warp_replace(S.open, 2 * H, S.c_d[i], id, lane, WL);
         }
     }
     PA_TICK(1);
@@ -365,13 +414,15 @@ __device__ __forceinline__ void search_stage(const RefineArgs &A, const RefShare
     // neighbour buffers.  Per expansion one CTA-wide barrier: behind it the heap
     // thread has popped node i (or ended the search) and -- when speculating --
     // the gather warps have prepared the node they expected.
-    if (tid == 0) {
-        const HeapEntry u = heap_pop(S.open, 2 * H);
+    if (w == 0) {
+        const HeapEntry u = warp_pop(S.open, 2 * H, lane, WL);
         const bool stop = max_iter <= 0 || u.v < 0 || u.k >= -S.buf[1].k;
-        ctl->pop_u[0] = stop ? -1 : u.v;
-        ctl->root_k[0] = S.open[1].k;
-        ctl->root_v[0] = S.open[1].v;
-        ctl->guess[0] = ctl->guess[1] = -2;
+        if (lane == 0) {
+            ctl->pop_u[0] = stop ? -1 : u.v;
+            ctl->root_k[0] = S.open[1].k;
+            ctl->root_v[0] = S.open[1].v;
+            ctl->guess[0] = ctl->guess[1] = -2;
+        }
     }
     PA_TICK(2);
     for (int step = 0; step < max_iter; ++step) {
@@ -385,7 +436,7 @@ __device__ __forceinline__ void search_stage(const RefineArgs &A, const RefShare
             __syncthreads();
         }
         PA_TICK(3);
-        if (tid == 0) {
+        if (w == 0) {
             // heap_update (:23-39) in row order, then the next pop (:84-90)
             const int n_new = ctl->n_new[p];
             const int32_t *nb_id = S.nb_id + p * kMaxDegree;
@@ -395,17 +446,19 @@ __device__ __forceinline__ void search_stage(const RefineArgs &A, const RefShare
             for (int j = 0; j < n_new; ++j) {
                 const float dist = nb_d[j];
                 if (dist >= -S.buf[1].k) continue;
-                heap_pushpop(S.buf, H, -dist, nb_id[j]);
-                heap_replace(S.open, 2 * H, dist, nb_id[j]);
+                warp_pushpop(S.buf, H, -dist, nb_id[j], lane, WL);
+                warp_replace(S.open, 2 * H, dist, nb_id[j], lane, WL);
             }
             if (step + 1 < max_iter) {
-                const HeapEntry nx = heap_pop(S.open, 2 * H);
+                const HeapEntry nx = warp_pop(S.open, 2 * H, lane, WL);
                 const bool stop = nx.v < 0 || nx.k >= -S.buf[1].k;
-                ctl->pop_u[p ^ 1] = stop ? -1 : nx.v;
-                ctl->root_k[p ^ 1] = S.open[1].k;
-                ctl->root_v[p ^ 1] = S.open[1].v;
+                if (lane == 0) {
+                    ctl->pop_u[p ^ 1] = stop ? -1 : nx.v;
+                    ctl->root_k[p ^ 1] = S.open[1].k;
+                    ctl->root_v[p ^ 1] = S.open[1].v;
+                }
             }
-        } else if (w > 0 && speculate && step + 1 < max_iter) {
+        } else if (speculate && step + 1 < max_iter) {
             // the node the next pop returns unless it ends the search: the first
             // new neighbour with the smallest distance if that is below the root
             // the open heap had after this expansion's pop, else that root
@@ -432,19 +485,21 @@ __device__ __forceinline__ void search_stage(const RefineArgs &A, const RefShare
     // :139-162: the seeds join the result heap; all but k_out are dropped; what is
     // left comes out worst first and is stored ascending
     const int n_real = min(k_out, H);
-    if (tid == 0) {
+    if (w == 0) {
         for (int i = 0; i < n_seed; ++i) {
             const int id = S.c_id[i];
-            if (id >= 0) heap_pushpop(S.buf, H, -S.c_d[i], id);
+            if (id >= 0) warp_pushpop(S.buf, H, -S.c_d[i], id, lane, WL);
         }
-        for (int i = k_out; i < H; ++i) heap_pop(S.buf, H);
+        for (int i = k_out; i < H; ++i) warp_pop(S.buf, H, lane, WL);
     }
     __syncthreads();  // every reader of the seeds is done
-    if (tid == 0) {
+    if (w == 0) {
         for (int i = 0; i < n_real; ++i) {
-            const HeapEntry e = heap_pop(S.buf, H);
-            S.c_id[k_out - i - 1] = e.v;
-            S.c_d[k_out - i - 1] = -e.k;
+            const HeapEntry e = warp_pop(S.buf, H, lane, WL);
+            if (lane == 0) {
+                S.c_id[k_out - i - 1] = e.v;
+                S.c_d[k_out - i - 1] = -e.k;
+            }
         }
     }
     // pops of an exhausted heap give (-1, key +inf): the leading pads
