@@ -300,6 +300,19 @@ def cpu_baseline_leg(w, index, queries, truth, ef_gpu, repeats=3):
                     pipe["gpu_stage2_then_upstream_stage3"] = {
                         "recall": round(recall_at(oI, truth[:w.n_queries], k), 4),
                         "refine_qps": round(q.size(0) / dt2, 1)}
+                if ref is not None:
+                    # host queries in -> top-k out with upstream's traverse_refine as the
+                    # consumer, chunks of 256 on the stage's slots: the host refines one
+                    # chunk while the GPU works on the next ones
+                    n_e2e = min(q.size(0), 2048)
+                    index.search(qp[:n_e2e], k, e, chunk_size=256, refine=ref.traverse_refine)
+                    t0 = time.perf_counter()
+                    eI, _ = index.search(qp[:n_e2e], k, e, chunk_size=256,
+                                         refine=ref.traverse_refine)
+                    dt3 = time.perf_counter() - t0
+                    pipe["e2e_upstream_refine_overlapped"] = {
+                        "recall": round(recall_at(eI, truth[:n_e2e], k), 4),
+                        "qps": round(n_e2e / dt3, 1), "chunk": 256}
     # upstream's own CUDA traversal kernel on this GPU, same tensors, same entries, at
     # the operating ef: the recompiled-reference number the kernel here is held against
     upstream_ms = None
