@@ -124,3 +124,77 @@ def test_heap_size_dispatch(oracle_lib):
              257: 256, 2048: 256, 2049: -1}
     for ef, h in table.items():
         assert oracle_lib.heap_size_for(ef) == h
+
+
+def test_refine_in_the_kernels_summation_order_pinned_to_upstream(oracle_lib, ref_ext, golden):
+    """``refine_ex(gpu_order=True)`` is what the refinement kernel is compared with
+    bit for bit; this pins it to upstream's ``traverse_refine`` itself (AVX2 order,
+    -ffast-math): same ids for >= 99.5 % of the entries, distances within 1e-5
+    relative, and the same rewritten handoff.  ``gpu_order=False`` is ``refine``."""
+    p = golden["problem"]
+    x, q = p["full"], p["query"]
+    g = torch.Generator().manual_seed(5)
+    B, k = q.size(0), 10
+    d_p = x.size(1) // 2 // 8 * 8
+    sub = [p["indptr"], p["indices"]]
+    full = [p["full_indptr"], p["full_indices"]]
+    for ef in (16, 48, 128):
+        n = 4 * ef
+        ids = p["nodelist"][torch.randint(p["nodelist"].numel(), (B, n), generator=g)]
+        ids[:, ::7] = -1                                          # pads inside the handoff
+        dist = ((q.unsqueeze(1) - x[ids.clamp_min(0)])[:, :, :d_p] ** 2).sum(-1).contiguous()
+        dist[ids < 0] = float("inf")
+        u_I = torch.empty(B, k, dtype=torch.long); u_D = torch.empty(B, k)
+        uI, uD = ids.clone(), dist.clone()
+        ref_ext.traverse_refine(u_I, u_D, uI, uD, uI, uD, sub, full, x, q, ef, d_p)
+        gI, gD = ids.clone(), dist.clone()
+        o_I, o_D, st = oracle_lib.refine_ex(gI, gD, sub, full, x, q, k, ef, d_p, gpu_order=True,
+                                            with_stats=True)
+        assert (o_I == u_I).float().mean().item() >= 0.995, ef
+        same = o_I == u_I
+        assert ((o_D - u_D).abs() <= 1e-5 * u_D.abs() + 1e-7)[same].all()
+        assert (gI == uI).float().mean().item() >= 0.995           # stage-2 rows
+        assert (st[:, 0] <= 2).all() and (st[:, 2] <= 2 * ef).all()
+        aI, aD = ids.clone(), dist.clone()
+        a_I, a_D = oracle_lib.refine_ex(aI, aD, sub, full, x, q, k, ef, d_p, gpu_order=False)
+        bI, bD = ids.clone(), dist.clone()
+        b_I, b_D = oracle_lib.refine(bI, bD, sub, full, x, q, k, ef, d_p)
+        assert torch.equal(a_I, b_I) and torch.equal(a_D, b_D) and torch.equal(aI, bI)
+        # stage 2 alone leaves exactly the rows the two-stage call leaves in the buffer
+        sI, sD = ids.clone(), dist.clone()
+        oracle_lib.refine_ex(sI, sD, sub, full, x, q, k, ef, d_p, gpu_order=True, stages=2)
+        assert torch.equal(sI, gI) and torch.equal(sD.view(torch.int32), gD.view(torch.int32))
+
+
+def test_warp_order_distance(oracle_lib):
+    g = torch.Generator().manual_seed(9)
+    for d, off in ((768, 0), (768, 128), (96, 64), (200, 96), (64, 0), (132, 4)):
+        q = torch.randn(d, generator=g)
+        x = torch.randn(d, generator=g)
+        want = ((q.double() - x.double())[off:] ** 2).sum().item()
+        got = oracle_lib.warp_distance(q, x, off)
+        assert abs(got - want) <= 2e-6 * max(want, 1e-30), (d, off)
+
+
+def test_cpu_heap_sizes(oracle_lib):
+    # extension/traverse_cpu.cpp:228-254
+    table = {1: 16, 16: 16, 17: 32, 33: 48, 49: 64, 65: 96, 97: 128, 129: 192, 193: 256,
+             257: 384, 385: 512, 513: 1024, 1025: 2048, 2049: -1}
+    for ef, h in table.items():
+        assert oracle_lib.cpu_heap_size_for(ef) == h
+    from pilotann_b200 import _C
+    for ef, h in table.items():
+        assert _C.lib().pa_cpu_heap_size_for(ef) == h
+
+
+def test_consumer_hook_validation():
+    import pilotann_b200
+    assert pilotann_b200.get_refine() == "gpu"
+    with pytest.raises(RuntimeError):
+        pilotann_b200.set_refine("cpu")
+    f = lambda *a: None
+    pilotann_b200.set_refine(f)
+    assert pilotann_b200.get_refine() is f
+    pilotann_b200.set_refine(None)
+    assert pilotann_b200.get_refine() is None
+    pilotann_b200.set_refine("gpu")
