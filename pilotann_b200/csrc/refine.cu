@@ -20,7 +20,7 @@
 // pop will return is known as soon as the distances of the current expansion are
 // (it is the better of the open heap's root and the best new neighbour -- a new
 // key below the root always sifts up to the root, equal keys never pass it), so
-// the gather warps start on that node while the heap thread still inserts the
+// the gather warps start on that node while the heap warp still inserts the
 // current expansion's neighbours and pops.  The pop then either confirms the
 // node or ends the search (when the best new neighbour is not admitted to the
 // heaps the next pop fails the stop test), in which case the speculative marks
@@ -54,7 +54,9 @@ constexpr int kGatherWarps = kRefWarps - 1;  // warp 0 runs the heaps
 #define PA_REFINE_MIN_CTAS 7
 #endif
 // PA_REFINE_PROFILE=1 (experiments only): thread 0 accumulates clock deltas per
-// phase into stats[b * 16 + 4 ..]; the stats rows are then 16 ints wide.
+// phase into stats[b * 16 + 4 ..]; the stats rows are then 16 ints wide.  The
+// compiler may move a clock read across a barrier, so a wait can land in the
+// neighbouring phase's count.
 #ifndef PA_REFINE_PROFILE
 #define PA_REFINE_PROFILE 0
 #endif
@@ -289,7 +291,7 @@ struct RefShared {
     float *stage;      // [kRefWarps][d] one staged vector row per warp
 };
 
-// What the heap thread publishes after a pop, and the gather side's guess.
+// What the heap warp publishes after a pop, and the gather side's guess.
 struct RefCtl {
     int pop_u[2];       // node popped for expansion i (slot i & 1), -1: the search ends
     float root_k[2];    // open heap's root right after that pop
@@ -362,7 +364,7 @@ __device__ __forceinline__ void gather_node(const RefineArgs &A, const RefShared
 // them), the result (k_out entries, ascending behind (-1, -inf) pads) back into
 // c_id / c_d.  `from` < d: the seeds' distances are first completed over dims
 // [from, d).  Returns expansions and evaluations through n_expand / n_eval
-// (thread 0).
+// (warp 0).
 __device__ __forceinline__ void search_stage(const RefineArgs &A, const RefShared &S,
                                              const RefGraph &G, uint8_t *vis, uint8_t marker,
                                              int n_seed, int from, int max_iter, int k_out,
@@ -412,7 +414,7 @@ __device__ __forceinline__ void search_stage(const RefineArgs &A, const RefShare
     PA_TICK(1);
     // :82-136.  Expansion i uses slot i & 1 of the control block and of the
     // neighbour buffers.  Per expansion one CTA-wide barrier: behind it the heap
-    // thread has popped node i (or ended the search) and -- when speculating --
+    // warp has popped node i (or ended the search) and -- when speculating --
     // the gather warps have prepared the node they expected.
     if (w == 0) {
         const HeapEntry u = warp_pop(S.open, 2 * H, lane, WL);

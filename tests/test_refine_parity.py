@@ -199,3 +199,41 @@ def test_rejections():
     h = ctypes.c_void_p()
     assert lib.pa_visited_pool_create(ctypes.byref(h), 100, 0) == _C.PA_ERR_ARG
     assert lib.pa_visited_pool_bytes(1000, 4) == 4 * 1008 + 16
+
+
+def test_large_ef_and_wide_rows(oracle_lib):
+    """ef_search 1024: heaps of 1024 / 2048 entries and a 4096-entry handoff row (more
+    shared memory than a CTA gets by default, so the launch opts in), the traversal
+    pads the handoff beyond its 256-entry heaps with (-1, -inf); and a degree-64
+    sub-graph (two 32-slot chunks per adjacency row)."""
+    from pilotann_b200 import extension
+    from helpers import make_problem
+    k = 10
+    for ef, n_nb in ((1024, 32), (64, 64)):
+        B, d, d_p = 48, 64, 32
+        p = make_problem(n=6000, d=d, n_nb=n_nb, ratio=0.5, batch=B, n_init=32, seed=61)
+        full = p["full"]
+        reduced = p["storage"][:, :d_p].contiguous()
+        q = p["query"]
+        g = torch.Generator().manual_seed(3)
+        ids = p["nodelist"][torch.randint(p["nodelist"].numel(), (B, 32), generator=g)]
+        init_D = ((q[:, :d_p].unsqueeze(1) - full[ids][:, :, :d_p]) ** 2).sum(-1).contiguous()
+        nbr, row_of = extension.pack_graph(p["indptr"].cuda(), p["indices"].cuda(),
+                                           p["mapping"].cuda(), reduced.size(0), n_nb)
+        hI = torch.empty(B, 4, ef, dtype=torch.int64, device="cuda")
+        hD = torch.empty(B, 4, ef, device="cuda")
+        extension.traverse_packed(hI, hD, nbr, row_of, reduced.cuda(), q[:, :d_p].contiguous().cuda(),
+                                  ids.cuda(), init_D.cuda(), n_nb)
+        full_nbr = extension.pack_fullgraph(p["full_indptr"].cuda(), p["full_indices"].cuda(), n_nb)
+        pool = extension.VisitedPool(full.size(0), 16)
+        st = torch.zeros(B, 4, dtype=torch.int32, device="cuda")
+        t_I, t_D = extension.refine(hI, hD, q.cuda(), full.cuda(), nbr, row_of, full_nbr, pool, ef,
+                                    d_p, k=k, stats=st)
+        torch.cuda.synchronize()
+        w_I, w_D, w_st = oracle_lib.refine_ex(hI.reshape(B, -1).cpu(), hD.reshape(B, -1).cpu(),
+                                              [p["indptr"], p["indices"]],
+                                              [p["full_indptr"], p["full_indices"]], full, q, k, ef,
+                                              d_p, gpu_order=True, with_stats=True)
+        assert torch.equal(t_I.cpu(), w_I), (ef, n_nb)
+        assert torch.equal(t_D.cpu().view(torch.int32), w_D.view(torch.int32))
+        assert torch.equal(st.cpu(), w_st)

@@ -201,3 +201,20 @@ def test_submit_wait_slots(small_index):
     assert c[0].shape == (64, 10) and c[0].data_ptr() == addr
     top_I, _ = index.search(q[:64], 10, ef)
     assert torch.equal(c[0], top_I)
+
+
+def test_ragged_chunks_and_empty_submit(small_index):
+    index, x, q, w = small_index
+    stage = index.stage
+    ef, k = 32, 7
+    want_I, want_D, _ = stage.search_host(q, ef, k=k)
+    got_I, got_D, _ = stage.search_host(q, ef, chunk=100, k=k)        # 100 + 100 + 56
+    assert torch.equal(want_I, got_I) and torch.equal(want_D, got_D)
+    h_I, _, _ = stage.search_host(q, ef, chunk=96)
+    h2_I, _, _ = stage.search_host(q, ef)
+    assert torch.equal(h_I, h2_I)
+    stage.submit(1, q[:0].contiguous(), ef, k=k)                       # nothing to do
+    out = stage.wait(1)
+    assert out[0].shape == (0, k)
+    with pytest.raises(RuntimeError):                                  # k beyond the row
+        stage.search_host(q, ef, k=4 * ef + 1)
