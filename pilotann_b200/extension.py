@@ -482,10 +482,13 @@ def pipeline(graph, subgraph, subgraph_cuda, storage, storage_cuda, query, query
              initial_I, initial_D, n_neighbors: int, ef_search: int, d_principle: int, k: int,
              chunk_size: int):
     """``extension.pipeline`` with upstream's positional order
-    (``extension/entry.cpp:48-56``, ``extension/pipeline_cpu.cpp:32-145``): chunks
-    of ``chunk_size`` queries alternate over two side streams; returns
+    (``extension/entry.cpp:48-56``, ``extension/pipeline_cpu.cpp:32-145``); returns
     ``[topk_I int64 [B, k], topk_D f32 [B, k]]`` on the CPU, ascending.  Who turns
-    the candidates into the top-k is set by :func:`set_refine`."""
+    the candidates into the top-k is set by :func:`set_refine`.  With a CPU
+    consumer, chunks of ``chunk_size`` queries alternate over two side streams and
+    the consumer refines one chunk while the GPU works on the next; with the GPU
+    consumer ``chunk_size`` is only checked (upstream requires it to divide the
+    batch) and the batch goes through in large pieces."""
     if len(graph) != 2 or len(subgraph) != 2 or len(subgraph_cuda) != 3:
         raise RuntimeError("graph / subgraph / subgraph_cuda must hold 2 / 2 / 3 tensors")
     _check_cuda("query_cuda", query_cuda, 2, torch.float32)
@@ -499,8 +502,6 @@ def pipeline(graph, subgraph, subgraph_cuda, storage, storage_cuda, query, query
                            "pilotann_b200.set_refine(\"gpu\") or set_refine(<traverse_refine>)")
     dev = query_cuda.device
     n_streams = _N_PIPE_STREAMS
-    bs = _pipe_set(dev, chunk_size, ef_search, k)
-    streams = bs["streams"]
     topk_I = torch.empty(batch, k, dtype=torch.int64, pin_memory=True)
     topk_D = torch.empty(batch, k, dtype=torch.float32, pin_memory=True)
     n_chunks = batch // chunk_size
@@ -513,16 +514,26 @@ def pipeline(graph, subgraph, subgraph_cuda, storage, storage_cuda, query, query
                       initial_D[lo:hi], n_neighbors)
 
     if consumer == "gpu":
+        # nothing on the host to overlap with: chunking would only shorten the launches
+        # (a 128-query launch lasts almost as long as a 1024-query one), so the whole
+        # batch goes through in pieces of up to 4096 queries on the two side streams
+        piece = batch
+        while piece > 4096 and piece % 2 == 0:
+            piece //= 2
+        bs = _pipe_set(dev, piece, ef_search, k)
+        streams = bs["streams"]
         res = _resident_for(graph, storage, subgraph_cuda, storage_cuda.size(0), n_neighbors,
-                            chunk_size, dev)
+                            piece, dev)
         q_full = query.to(dev, non_blocking=True)
         ready.record(torch.cuda.current_stream(dev))
-        for i in range(n_chunks):
+        for i in range(batch // piece):
             slot = i % n_streams
-            lo, hi = i * chunk_size, (i + 1) * chunk_size
+            lo, hi = i * piece, (i + 1) * piece
             with torch.cuda.stream(streams[slot]):
                 streams[slot].wait_event(ready)
-                traverse(slot, lo, hi)
+                traverse_cuda(bs["dev_I"][slot], bs["dev_D"][slot], subgraph_cuda[0],
+                              subgraph_cuda[1], subgraph_cuda[2], storage_cuda, query_cuda[lo:hi],
+                              initial_I[lo:hi], initial_D[lo:hi], n_neighbors)
                 refine(bs["dev_I"][slot], bs["dev_D"][slot], q_full[lo:hi], res["storage"],
                        res["packed"][0], res["packed"][1], res["full_nbr"], res["pools"][slot],
                        ef_search, d_principle, k=k, out=(bs["top_I"][slot], bs["top_D"][slot]))
@@ -535,6 +546,8 @@ def pipeline(graph, subgraph, subgraph_cuda, storage, storage_cuda, query, query
 
     # a CPU consumer: chunk i is launched, then chunk i - n_streams (long finished on
     # the GPU) is refined on the host while the GPU works on the chunks in between
+    bs = _pipe_set(dev, chunk_size, ef_search, k)
+    streams = bs["streams"]
     for i in range(n_chunks + n_streams):
         slot = i % n_streams
         if i >= n_streams:

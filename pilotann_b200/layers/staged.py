@@ -162,7 +162,7 @@ class IndexStaged(nn.Module):
 
         Who refines the candidates: ``refine`` if given, else what
         :func:`pilotann_b200.set_refine` chose.  ``"gpu"`` finishes on the device
-        (needs ``to(..., refine="gpu")``).  A callable with the signature of
+        (needs ``to(..., refine="gpu")``; ``chunk_size`` is not used then).  A callable with the signature of
         upstream's ``extension.traverse_refine`` runs on the host: chunks are
         submitted to the stage's slots and the callable refines one chunk while the
         GPU works on the next ones (upstream's overlap,
@@ -178,7 +178,17 @@ class IndexStaged(nn.Module):
             if not self.stage.has_full_graph:
                 raise RuntimeError('search: the index was moved to the device without '
                                    'refine="gpu"; pass refine=<traverse_refine>')
-            I, D, _ = self.stage.search_host(query, ef_search, chunk=chunk_size, k=k)
+            # nothing on the host to overlap with, so chunk_size plays no role: the
+            # batch goes through in pieces as large as the stage takes
+            cap = self.stage.max_batch
+            if B <= cap:
+                I, D, _ = self.stage.search_host(query, ef_search, k=k)
+                return I, D
+            I = torch.empty(B, k, dtype=torch.int64, pin_memory=True)
+            D = torch.empty(B, k, dtype=torch.float32, pin_memory=True)
+            for lo in range(0, B, cap):
+                self.stage.search_host(query[lo:lo + cap], ef_search, out_I=I[lo:lo + cap],
+                                       out_D=D[lo:lo + cap], k=k)
             return I, D
         stage = self.stage
         step = min(chunk_size if chunk_size > 0 else B, stage.slot_rows)

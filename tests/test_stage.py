@@ -173,6 +173,10 @@ def test_search_finishes_on_the_gpu_by_default(small_index, oracle_lib):
     dI, dD = index.stage.search_device(q.cuda(), ef, k=k)
     index.stage.synchronize()
     assert torch.equal(dI.cpu(), I)
+    # more queries than the stage takes at once
+    more_I, more_D = index.search(torch.cat([q, q[:100]]), k, ef)
+    assert torch.equal(more_I[:256], I) and torch.equal(more_I[256:], I[:100])
+    assert torch.equal(more_D[256:], D[:100])
 
 
 def test_submit_wait_slots(small_index):
