@@ -237,3 +237,38 @@ def test_large_ef_and_wide_rows(oracle_lib):
         assert torch.equal(t_I.cpu(), w_I), (ef, n_nb)
         assert torch.equal(t_D.cpu().view(torch.int32), w_D.view(torch.int32))
         assert torch.equal(st.cpu(), w_st)
+
+
+def test_shape_sweep_vs_oracle(oracle_lib):
+    """Odd shapes: dimensions that are not multiples of 128 (or of 32), d_principle
+    anywhere up to d, ef 1 (a 4-entry handoff under 16-entry heaps), heaps that are
+    not powers of two, k from 1 to the whole row -- all bit for bit."""
+    from pilotann_b200 import extension
+    from helpers import make_problem
+    g = torch.Generator().manual_seed(77)
+    shapes = [(8, 4, 1, 1), (8, 8, 3, 5), (20, 12, 16, 10), (64, 16, 17, 1), (100, 64, 33, 40),
+              (132, 128, 100, 25), (256, 64, 300, 50), (36, 36, 40, 160)]
+    for d, d_p, ef, k in shapes:
+        B = 24
+        p = make_problem(n=3000, d=d, ratio=0.5, batch=B, n_init=32, seed=80 + d)
+        full, q = p["full"], p["query"]
+        ids = p["nodelist"][torch.randint(p["nodelist"].numel(), (B, 4 * ef), generator=g)]
+        ids[torch.rand(B, 4 * ef, generator=g) < 0.15] = -1
+        dist = ((q[:, :d_p].unsqueeze(1) - full[ids.clamp_min(0)][:, :, :d_p]) ** 2).sum(-1)
+        dist[ids < 0] = float("inf")
+        dist = dist.contiguous()
+        reduced = p["storage"][:, :d_p].contiguous()
+        nbr, row_of = extension.pack_graph(p["indptr"].cuda(), p["indices"].cuda(),
+                                           p["mapping"].cuda(), reduced.size(0), 32)
+        full_nbr = extension.pack_fullgraph(p["full_indptr"].cuda(), p["full_indices"].cuda(), 32)
+        pool = extension.VisitedPool(full.size(0), 7)
+        st = torch.zeros(B, 4, dtype=torch.int32, device="cuda")
+        t_I, t_D = extension.refine(ids.cuda(), dist.cuda(), q.cuda(), full.cuda(), nbr, row_of,
+                                    full_nbr, pool, ef, d_p, k=k, stats=st)
+        torch.cuda.synchronize()
+        w_I, w_D, w_st = oracle_lib.refine_ex(ids.clone(), dist.clone(), [p["indptr"], p["indices"]],
+                                              [p["full_indptr"], p["full_indices"]], full, q, k, ef,
+                                              d_p, gpu_order=True, with_stats=True)
+        assert torch.equal(t_I.cpu(), w_I), (d, d_p, ef, k)
+        assert torch.equal(t_D.cpu().view(torch.int32), w_D.view(torch.int32)), (d, d_p, ef, k)
+        assert torch.equal(st.cpu(), w_st), (d, d_p, ef, k)
