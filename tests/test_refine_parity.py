@@ -272,3 +272,33 @@ def test_shape_sweep_vs_oracle(oracle_lib):
         assert torch.equal(t_I.cpu(), w_I), (d, d_p, ef, k)
         assert torch.equal(t_D.cpu().view(torch.int32), w_D.view(torch.int32)), (d, d_p, ef, k)
         assert torch.equal(st.cpu(), w_st), (d, d_p, ef, k)
+
+
+def test_replay_of_upstream_fixtures():
+    """Outputs of upstream ``traverse_refine`` recorded by tests/golden/make_golden.py
+    (CPU, no GPU involved), replayed through the refinement kernel without the
+    upstream module: top-k, and the handoff rows the sub-graph stage leaves."""
+    from pathlib import Path
+    from pilotann_b200 import extension
+    gold = torch.load(Path(__file__).parent / "golden" / "golden_cpu.pt")
+    p = gold["problem"]
+    n = p["full"].size(0)
+    d_sub = p["storage"].size(1)
+    nbr, row_of = extension.pack_graph(p["indptr"].cuda(), p["indices"].cuda(), p["mapping"].cuda(),
+                                       p["storage"].size(0), 32)
+    full_nbr = extension.pack_fullgraph(p["full_indptr"].cuda(), p["full_indices"].cuda(), 32)
+    pool = extension.VisitedPool(n, 8)
+    assert d_sub == p["full"].size(1)
+    for ef, fx in gold["refine"].items():
+        k = fx["out_I"].size(1)
+        args = (fx["cand_I"].cuda(), fx["cand_D"].cuda(), p["query"].cuda(), p["full"].cuda(), nbr,
+                row_of)
+        t_I, t_D = extension.refine(*args, full_nbr, pool, ef, fx["d_principle"], k=k)
+        s_I, s_D = extension.refine(*args, None, pool, ef, fx["d_principle"], k=None)
+        torch.cuda.synchronize()
+        assert (t_I.cpu() == fx["out_I"]).float().mean().item() >= 0.995, ef
+        assert torch.allclose(t_D.cpu(), fx["out_D"], rtol=1e-5, atol=1e-6)
+        assert (s_I.cpu() == fx["buffer_I"]).float().mean().item() >= 0.995
+        fin = torch.isfinite(fx["buffer_D"])
+        assert torch.equal(fin, torch.isfinite(s_D.cpu()))
+        assert torch.allclose(s_D.cpu()[fin], fx["buffer_D"][fin], rtol=1e-5, atol=1e-6)
