@@ -505,7 +505,7 @@ def kernel_only(which, w, index, queries, device, ef):
         storage = index.storage.to(device)
         full_nbr = extension.pack_fullgraph(index.fullgraph.indptr.to(device),
                                             index.fullgraph.indices.to(device), index.n_neighbors)
-        pool = extension.VisitedPool(storage.size(0), min(B, 1036), device)
+        pool = extension.VisitedPool(storage.size(0), min(B, extension.refine_wave(storage.size(1), device)), device)
         tI = torch.empty(B, k, dtype=torch.int64, device=device)
         tD = torch.empty(B, k, dtype=torch.float32, device=device)
         call = lambda: extension.refine(oI, oD, rot, storage, index.packed_nbr, index.row_of,
@@ -758,7 +758,7 @@ def main():
     n_init = EP_I.size(1)
     algo_bytes = (C * 4 * w.d_principle + E * 4 * index.n_neighbors
                   + B * (4 * w.d_principle + 12 * n_init + 48 * ef))
-    pool = extension.VisitedPool(index.storage.size(0), min(B, 1036), device)
+    pool = extension.VisitedPool(index.storage.size(0), min(B, extension.refine_wave(index.storage.size(1), device)), device)
     r_stats = torch.zeros(B, 4, dtype=torch.int32, device=device)
 
     def refine_call():

@@ -176,6 +176,10 @@ int pa_visited_pool_slots(const pa_visited_pool *pool);
  * Distances are summed in this kernel's own order (see csrc/refine.cu); against
  * upstream's AVX2 build they agree within 1e-5 relative. */
 int pa_cpu_heap_size_for(int ef_search);
+/* Refinement CTAs (one query each) an SM holds at once for vectors of d_model floats:
+ * the visited slots worth having per SM.  The counterpart upstream is the size of its
+ * BitmaskPool, one bitmask per OpenMP thread (traverse_cpu.cpp:208-226). */
+int pa_refine_ctas_per_sm(int d_model);
 int pa_pack_fullgraph(int32_t *full_nbr, const int64_t *indptr, const int64_t *indices,
                       int64_t n_nodes, int degree, void *stream);
 int pa_refine(int64_t *out_I, float *out_D, const int64_t *cand_I, const float *cand_D,

@@ -22,7 +22,7 @@ SYMBOLS = (
     "pa_stage_search", "pa_stage_search_device", "pa_stage_synchronize", "pa_stage_stream",
     "pa_launch_count", "pa_search_reduced_noalloc", "pa_device_status", "pa_route_ws", "pa_route_workspace_floats",
     "pa_selftest_bounded_wait", "pa_visited_pool_bytes", "pa_visited_pool_create",
-    "pa_visited_pool_destroy", "pa_visited_pool_slots", "pa_cpu_heap_size_for",
+    "pa_visited_pool_destroy", "pa_visited_pool_slots", "pa_cpu_heap_size_for", "pa_refine_ctas_per_sm",
     "pa_pack_fullgraph", "pa_refine", "pa_stage_attach_refine", "pa_stage_search_ex",
     "pa_stage_search_device_ex", "pa_stage_slot_rows", "pa_stage_submit", "pa_stage_wait",
 )
@@ -93,6 +93,8 @@ def lib() -> ctypes.CDLL:
     L.pa_visited_pool_slots.restype = c_int
     L.pa_cpu_heap_size_for.argtypes = [c_int]
     L.pa_cpu_heap_size_for.restype = c_int
+    L.pa_refine_ctas_per_sm.argtypes = [c_int]
+    L.pa_refine_ctas_per_sm.restype = c_int
     L.pa_pack_fullgraph.argtypes = [P, P, P, c_int64, c_int, P]
     L.pa_pack_fullgraph.restype = c_int
     L.pa_refine.argtypes = [P, P, P, P, P, P, P, P, c_int, P, c_int, c_int64, c_int64, c_int,

@@ -54,6 +54,7 @@ int project_launch(float *out, const float *query, const float *VT, int64_t batc
 void pool_view(const pa_visited_pool *pool, uint8_t **marks, int32_t **epoch, int64_t *slot_stride,
                int *n_slots, int64_t *n_nodes);
 
+int refine_ctas_per_sm(int d_model);
 int refine_enqueue(int64_t *out_I, float *out_D, const int64_t *cand_I, const float *cand_D,
                    const float *query, int64_t ldq, const float *storage_full,
                    const int32_t *packed_nbr, const int32_t *row_of, int n_neighbors,

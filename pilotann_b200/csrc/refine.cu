@@ -12,10 +12,11 @@
 //            with full-dimension distances, up to 2 * ef expansions, top-k out.
 //
 // The candidates are consumed where the traversal left them, in HBM; nothing of
-// the handoff crosses PCIe.  One CTA of five warps per query, persistent: CTA i
+// the handoff crosses PCIe.  One CTA of five warps (three for rows of at most 512
+// bytes) per query, persistent: CTA i
 // owns slot i of the visited-set pool (visited.cu) and walks the batch with
 // stride gridDim.x.  Warp 0 is the heap warp (it runs upstream's heap routines),
-// warps 1-4 gather: adjacency row, visited marks, vector rows,
+// the other warps gather: adjacency row, visited marks, vector rows,
 // distances.  In the full-graph stage the two sides overlap: the node the next
 // pop will return is known as soon as the distances of the current expansion are
 // (it is the better of the open heap's root and the best new neighbour -- a new
@@ -47,9 +48,30 @@
 
 namespace pa {
 
-constexpr int kRefThreads = 160;
-constexpr int kRefWarps = kRefThreads / 32;
-constexpr int kGatherWarps = kRefWarps - 1;  // warp 0 runs the heaps
+// Warp 0 runs the heaps, the other warps gather.  The kernel is compiled for CTAs of
+// up to five warps; vector rows of at most 512 bytes are served by two gather warps
+// (96 threads), which lets twelve instead of seven queries share an SM -- at those
+// sizes the heap warp, not the gather, sets the pace of a query -- or by three when
+// the batch leaves room for them (nine queries per SM).
+#ifndef PA_REFINE_WIDE_THREADS
+#define PA_REFINE_WIDE_THREADS 160
+#endif
+#ifndef PA_REFINE_NARROW_THREADS
+#define PA_REFINE_NARROW_THREADS 96
+#endif
+#ifndef PA_REFINE_NARROW_DIM
+#define PA_REFINE_NARROW_DIM 128
+#endif
+constexpr int kRefThreads = 160;  // what the kernel is compiled for
+constexpr int kRefThreadsWide = PA_REFINE_WIDE_THREADS;
+constexpr int kRefThreadsNarrow = PA_REFINE_NARROW_THREADS;
+constexpr int kNarrowMaxDim = PA_REFINE_NARROW_DIM;
+static_assert(kRefThreadsWide <= kRefThreads && kRefThreadsNarrow <= kRefThreads &&
+                  kRefThreadsNarrow >= 64 && kRefThreadsWide % 32 == 0 && kRefThreadsNarrow % 32 == 0,
+              "a heap warp plus one to four gather warps");
+__host__ __device__ inline int ref_threads_for(int d) {
+    return d <= kNarrowMaxDim ? kRefThreadsNarrow : kRefThreadsWide;
+}
 #ifndef PA_REFINE_MIN_CTAS
 #define PA_REFINE_MIN_CTAS 7
 #endif
@@ -288,7 +310,7 @@ struct RefShared {
     float *c_d;
     int32_t *nb_id;    // [2][kMaxDegree] unvisited neighbours of an expanded node
     float *nb_d;       //                 (two expansions are in flight)
-    float *stage;      // [kRefWarps][d] one staged vector row per warp
+    float *stage;      // [warps][d] one staged vector row per warp
 };
 
 // What the heap warp publishes after a pop, and the gather side's guess.
@@ -302,7 +324,7 @@ struct RefCtl {
 };
 
 __device__ __forceinline__ void gather_sync() {  // the gather warps only
-    asm volatile("bar.sync 1, %0;" ::"n"(32 * kGatherWarps) : "memory");
+    asm volatile("bar.sync 1, %0;" ::"r"(static_cast<int>(blockDim.x) - 32) : "memory");
 }
 
 // The gather half of one expansion (traverse_cpu.cpp:105-135 without the heap
@@ -343,8 +365,9 @@ __device__ __forceinline__ void gather_node(const RefineArgs &A, const RefShared
     const int n_new = ctl->n_new[p];
     // three rows per warp and trip: two through registers, one staged by cp.async
     float *stage = S.stage + (gw + 1) * d;
-    for (int j = gw; j < n_new; j += 3 * kGatherWarps) {
-        const int j1 = j + kGatherWarps, j2 = j + 2 * kGatherWarps;
+    const int n_gw = static_cast<int>(blockDim.x >> 5) - 1;  // gather warps
+    for (int j = gw; j < n_new; j += 3 * n_gw) {
+        const int j1 = j + n_gw, j2 = j + 2 * n_gw;
         const int v0 = nb_id[j], v1 = j1 < n_new ? nb_id[j1] : v0;
         if (j2 < n_new) row_to_stage(stage, A.storage + static_cast<int64_t>(nb_id[j2]) * d, d, 0, lane);
         float r0, r1;
@@ -376,8 +399,9 @@ __device__ __forceinline__ void search_stage(const RefineArgs &A, const RefShare
     // distances completed over the trailing dims (:41-62), in place
     if (from < d) {
         float *stage = S.stage + w * d;
-        for (int i = w; i < n_seed; i += 3 * kRefWarps) {
-            const int i1 = i + kRefWarps, i2 = i + 2 * kRefWarps;
+        const int n_w = static_cast<int>(blockDim.x >> 5);
+        for (int i = w; i < n_seed; i += 3 * n_w) {
+            const int i1 = i + n_w, i2 = i + 2 * n_w;
             const int id0 = S.c_id[i], id1 = i1 < n_seed ? S.c_id[i1] : -1;
             const int id2 = i2 < n_seed ? S.c_id[i2] : -1;
             if (id0 < 0 && id1 < 0 && id2 < 0) continue;  // warp-uniform
@@ -395,10 +419,10 @@ __device__ __forceinline__ void search_stage(const RefineArgs &A, const RefShare
         }
     }
     // :65-68
-    for (int i = tid; i < H + 2; i += kRefThreads) S.buf[i] = HeapEntry{-CUDART_INF_F, -1};
-    for (int i = tid; i < 2 * H + 2; i += kRefThreads) S.open[i] = HeapEntry{CUDART_INF_F, -1};
+    for (int i = tid; i < H + 2; i += blockDim.x) S.buf[i] = HeapEntry{-CUDART_INF_F, -1};
+    for (int i = tid; i < 2 * H + 2; i += blockDim.x) S.open[i] = HeapEntry{CUDART_INF_F, -1};
     // :69-79, the marks (their order does not matter; the heap inserts below keep it)
-    for (int i = tid; i < n_seed; i += kRefThreads) {
+    for (int i = tid; i < n_seed; i += blockDim.x) {
         const int id = S.c_id[i];
         if (id >= 0) vis[id] = marker;
     }
@@ -505,7 +529,7 @@ __device__ __forceinline__ void search_stage(const RefineArgs &A, const RefShare
         }
     }
     // pops of an exhausted heap give (-1, key +inf): the leading pads
-    for (int i = tid; i < k_out - n_real; i += kRefThreads) {
+    for (int i = tid; i < k_out - n_real; i += blockDim.x) {
         S.c_id[i] = -1;
         S.c_d[i] = -CUDART_INF_F;
     }
@@ -538,15 +562,15 @@ __global__ void __launch_bounds__(kRefThreads, PA_REFINE_MIN_CTAS) refine_kernel
         int marker = ctl->marker;
         if (marker > 254) {
             uint4 *p = reinterpret_cast<uint4 *>(vis);
-            for (int64_t i = tid; i < A.slot_stride / 16; i += kRefThreads)
+            for (int64_t i = tid; i < A.slot_stride / 16; i += blockDim.x)
                 p[i] = make_uint4(0, 0, 0, 0);
             marker = 1;
         }
         __syncthreads();
         if (tid == 0) A.epoch[slot] = marker;
 
-        for (int i = tid; i < A.d; i += kRefThreads) S.q[i] = A.query[b * A.ldq + i];
-        for (int i = tid; i < A.n_cand; i += kRefThreads) {
+        for (int i = tid; i < A.d; i += blockDim.x) S.q[i] = A.query[b * A.ldq + i];
+        for (int i = tid; i < A.n_cand; i += blockDim.x) {
             const int64_t id = A.cand_I[b * A.n_cand + i];
             S.c_id[i] = (id < 0 || id >= A.n_nodes) ? -1 : static_cast<int32_t>(id);
             S.c_d[i] = A.cand_D[b * A.n_cand + i];
@@ -564,7 +588,7 @@ __global__ void __launch_bounds__(kRefThreads, PA_REFINE_MIN_CTAS) refine_kernel
                          min(1024, 2 * A.ef), A.k, true, ctl, st[2], st[3], prof, prof_t);
             k_out = A.k;
         }
-        for (int i = tid; i < k_out; i += kRefThreads) {
+        for (int i = tid; i < k_out; i += blockDim.x) {
             A.out_I[b * k_out + i] = S.c_id[i];
             A.out_D[b * k_out + i] = S.c_d[i];
         }
@@ -589,8 +613,17 @@ static int cpu_heap_size_for(int ef) {
     return -1;
 }
 
+// Refinement CTAs one SM holds at ef_search 128 (registers and shared memory): the
+// number of visited slots worth having per SM.
+int refine_ctas_per_sm(int d_model) {
+    const int by_registers = (64 * 1024) / (56 * ref_threads_for(d_model));
+    return by_registers < 12 ? by_registers : 12;  // shared memory: about 17 KB per CTA
+}
+
 static size_t refine_smem_bytes(int d, int H, int n_cand) {
-    return sizeof(float) * d * (1 + kRefWarps) + sizeof(HeapEntry) * (3 * H + 4) +
+    // one staged row per warp: a narrow CTA may be launched with up to four warps
+    const int warps = max(ref_threads_for(d), 128) / 32;
+    return sizeof(float) * d * (1 + warps) + sizeof(HeapEntry) * (3 * H + 4) +
            8 * static_cast<size_t>(n_cand) + 16 * kMaxDegree;
 }
 
@@ -607,7 +640,16 @@ static int refine_launch(const RefineArgs &A, int n_slots, cudaStream_t stream) 
     }
     const unsigned grid = static_cast<unsigned>(min(static_cast<int64_t>(A.batch),
                                                     static_cast<int64_t>(n_slots)));
-    refine_kernel<<<grid, kRefThreads, smem, stream>>>(A);
+    int threads = ref_threads_for(A.d);
+    if (threads == kRefThreadsNarrow && kRefThreadsNarrow == 96) {
+        static int sms[64] = {};
+        if (dev >= 0 && dev < 64) {
+            if (sms[dev] == 0)
+                PA_CUDA_TRY(cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev));
+            if (grid <= 9u * static_cast<unsigned>(sms[dev])) threads = 128;
+        }
+    }
+    refine_kernel<<<grid, threads, smem, stream>>>(A);
     count_launch();
     PA_CUDA_TRY(cudaGetLastError());
     return PA_OK;
@@ -687,6 +729,8 @@ __global__ void pack_full_kernel(int32_t *__restrict__ out, const int64_t *__res
 }  // namespace pa
 
 extern "C" int pa_cpu_heap_size_for(int ef_search) { return pa::cpu_heap_size_for(ef_search); }
+
+extern "C" int pa_refine_ctas_per_sm(int d_model) { return pa::refine_ctas_per_sm(d_model); }
 
 namespace pa {
 

@@ -358,7 +358,7 @@ extern "C" int pa_stage_attach_refine(pa_stage *st, const pa_refine_index *rx,
         // one wave of refinement CTAs: what the device holds at once
         int sms = 0;
         PA_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, st->device));
-        slots_per_stream = sms * 7;
+        slots_per_stream = sms * refine_ctas_per_sm(st->ix.d_model);
         if (slots_per_stream > st->max_batch) slots_per_stream = static_cast<int>(st->max_batch);
     }
     int rc = pa_visited_pool_create(&st->pool, st->ix.n_nodes,

@@ -336,6 +336,13 @@ def cpu_heap_size_for(ef_search: int) -> int:
     return int(_C.lib().pa_cpu_heap_size_for(ef_search))
 
 
+def refine_wave(d_model: int, device=None) -> int:
+    """Queries the refinement kernel works on at once on ``device``: the number of
+    visited slots (``VisitedPool``) worth allocating for one stream."""
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    return sms * int(_C.lib().pa_refine_ctas_per_sm(d_model))
+
+
 def refine(cand_I, cand_D, query, storage, packed_nbr, row_of, full_nbr, pool: VisitedPool,
            ef_search: int, d_principle: int, k: int | None = None, stats=None, out=None):
     """``traverse_refine`` (``extension/traverse_cpu.cpp:261-369``) on the GPU over
@@ -472,7 +479,7 @@ def _resident_for(graph, storage, subgraph_cuda, n_storage_sub: int, n_neighbors
         entry = {"refs": tuple(weakref.ref(t) for t in tensors), "stamp": stamp, "chunk": chunk,
                  "packed": packed, "full_nbr": full_nbr,
                  "storage": storage.to(dev).contiguous(),
-                 "pools": [VisitedPool(storage.size(0), min(chunk, 1036), dev)
+                 "pools": [VisitedPool(storage.size(0), min(chunk, refine_wave(storage.size(1), dev)), dev)
                            for _ in range(_N_PIPE_STREAMS)]}
         _resident[key] = entry
         return entry

@@ -274,6 +274,39 @@ def test_shape_sweep_vs_oracle(oracle_lib):
         assert torch.equal(st.cpu(), w_st), (d, d_p, ef, k)
 
 
+def test_three_warp_ctas_for_short_rows(oracle_lib):
+    """Rows of at most 128 floats and more queries than nine per SM: the kernel runs
+    with a heap warp and two gather warps (twelve CTAs per SM) instead of three or four.
+    Same bits as the oracle, and as the same queries refined in small batches (which
+    take the wider CTAs)."""
+    from pilotann_b200 import extension
+    from helpers import make_problem
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    B, d, d_p, ef, k = 9 * sms + 170, 64, 32, 24, 10
+    g = torch.Generator().manual_seed(5)
+    p = make_problem(n=3000, d=d, ratio=0.5, batch=B, n_init=32, seed=91)
+    full, q = p["full"], p["query"]
+    ids = p["nodelist"][torch.randint(p["nodelist"].numel(), (B, 4 * ef), generator=g)]
+    dist = ((q[:, :d_p].unsqueeze(1) - full[ids][:, :, :d_p]) ** 2).sum(-1).contiguous()
+    nbr, row_of = extension.pack_graph(p["indptr"].cuda(), p["indices"].cuda(), p["mapping"].cuda(),
+                                       p["storage"].size(0), 32)
+    full_nbr = extension.pack_fullgraph(p["full_indptr"].cuda(), p["full_indices"].cuda(), 32)
+    assert extension.refine_wave(d) == 12 * sms and extension.refine_wave(768) == 7 * sms
+    pool = extension.VisitedPool(full.size(0), B)
+    st = torch.zeros(B, 4, dtype=torch.int32, device="cuda")
+    args = (full.cuda(), nbr, row_of, full_nbr, pool, ef, d_p)
+    t_I, t_D = extension.refine(ids.cuda(), dist.cuda(), q.cuda(), *args, k=k, stats=st)
+    torch.cuda.synchronize()
+    w_I, w_D, w_st = oracle_lib.refine_ex(ids.clone(), dist.clone(), [p["indptr"], p["indices"]],
+                                          [p["full_indptr"], p["full_indices"]], full, q, k, ef,
+                                          d_p, gpu_order=True, with_stats=True)
+    assert torch.equal(t_I.cpu(), w_I)
+    assert torch.equal(t_D.cpu().view(torch.int32), w_D.view(torch.int32))
+    assert torch.equal(st.cpu(), w_st)
+    s_I, s_D = extension.refine(ids[:200].cuda(), dist[:200].cuda(), q[:200].cuda(), *args, k=k)
+    assert torch.equal(s_I, t_I[:200]) and torch.equal(s_D.view(torch.int32), t_D[:200].view(torch.int32))
+
+
 def test_replay_of_upstream_fixtures():
     """Outputs of upstream ``traverse_refine`` recorded by tests/golden/make_golden.py
     (CPU, no GPU involved), replayed through the refinement kernel without the
