@@ -75,17 +75,27 @@ __host__ __device__ inline int ref_threads_for(int d) {
 #ifndef PA_REFINE_MIN_CTAS
 #define PA_REFINE_MIN_CTAS 7
 #endif
-// PA_REFINE_PROFILE=1 (experiments only): thread 0 accumulates clock deltas per
-// phase into stats[b * 16 + 4 ..]; the stats rows are then 16 ints wide.  The
-// compiler may move a clock read across a barrier, so a wait can land in the
-// neighbouring phase's count.
+// PA_REFINE_PROFILE (experiments only): 1 = thread 0 (heap warp) accumulates clock
+// deltas per phase into stats[b * 24 + 4 ..] and thread 32 (first gather warp) into
+// stats[b * 24 + 12 ..]; 2 = thread 32 only.  The stats rows are then 24 ints wide.
+// A clock read may still move across a barrier, so a wait can land in the
+// neighbouring phase's count; and the heap warp's own clocks slow its heap routines
+// several times over while the gather warps run beside it -- read the heap warp's
+// cost from mode 2 (how long the gather warps wait for it).
 #ifndef PA_REFINE_PROFILE
 #define PA_REFINE_PROFILE 0
 #endif
 #if PA_REFINE_PROFILE
-#define PA_TICK(slot) do { if (threadIdx.x == 0) { const long long now__ = clock64(); prof[slot] += static_cast<int>(now__ - prof_t); prof_t = now__; } } while (0)
+__device__ __forceinline__ long long pinned_clock() {
+    long long t;
+    asm volatile("mov.u64 %0, %%clock64;" : "=l"(t)::"memory");
+    return t;
+}
+#define PA_TICK(slot) do { if (PA_REFINE_PROFILE == 1 && threadIdx.x == 0) { const long long now__ = pinned_clock(); prof[slot] += static_cast<int>(now__ - prof_t); prof_t = now__; } } while (0)
+#define PA_GTICK(slot) do { if (threadIdx.x == 32) { const long long now__ = pinned_clock(); prof[slot] += static_cast<int>(now__ - prof_t); prof_t = now__; } } while (0)
 #else
 #define PA_TICK(slot) do { } while (0)
+#define PA_GTICK(slot) do { } while (0)
 #endif
 constexpr int kMaxDegree = 64;
 constexpr unsigned kAll = 0xffffffffu;
@@ -280,6 +290,26 @@ __device__ __forceinline__ void two_rows(const float *__restrict__ r0, const flo
     o1 = butterfly(a1);
 }
 
+// One row over dims [from, d) with six stripes (768 floats) loaded before any
+// arithmetic: a row of up to 3 KB makes a single round trip.  Same order of
+// additions as two_rows.
+__device__ __forceinline__ float one_row(const float *__restrict__ r0, const float *q_s, int d,
+                                         int from, int lane) {
+    float a0 = 0.0f;
+    for (int o = from + 4 * lane; o < d; o += 768) {
+        float4 x0[6];
+#pragma unroll
+        for (int m = 0; m < 6; ++m)
+            x0[m] = o + 128 * m < d ? __ldg(reinterpret_cast<const float4 *>(r0 + o + 128 * m))
+                                    : make_float4(0, 0, 0, 0);
+#pragma unroll
+        for (int m = 0; m < 6; ++m)
+            if (o + 128 * m < d)
+                a0 = ref_stripe(a0, *reinterpret_cast<const float4 *>(q_s + o + 128 * m), x0[m]);
+    }
+    return butterfly(a0);
+}
+
 // A third row rides along without registers: cp.async copies it into the warp's
 // own staging buffer while the two register rows make their round trips; every
 // lane later reads back exactly the 16-byte pieces it copied itself.
@@ -333,7 +363,10 @@ __device__ __forceinline__ void gather_sync() {  // the gather warps only
 // Called by all gather warps.
 __device__ __forceinline__ void gather_node(const RefineArgs &A, const RefShared &S,
                                             const RefGraph &G, uint8_t *vis, uint8_t marker,
-                                            RefCtl *ctl, int u, int p, int gw, int lane) {
+                                            RefCtl *ctl, int u, int p, int gw, int lane, int *prof,
+                                            long long &prof_t) {
+    (void)prof; (void)prof_t;
+    PA_GTICK(0);  // since the last tick: prediction, barriers, waiting for the heap warp
     int32_t *nb_id = S.nb_id + p * kMaxDegree;
     float *nb_d = S.nb_d + p * kMaxDegree;
     const int d = A.d;
@@ -347,6 +380,7 @@ __device__ __forceinline__ void gather_node(const RefineArgs &A, const RefShared
             if (!ended && slot < G.degree)
                 v = __ldg(G.nbr + row * G.row_stride + static_cast<int64_t>(slot) * G.elem_stride);
             const unsigned end_mask = __ballot_sync(kAll, v < 0 && v != kDupTag);
+            PA_GTICK(1);  // adjacency row
             const int first_end = end_mask ? __ffs(end_mask) - 1 : 32;
             const bool live = lane < first_end && v >= 0;
             bool fresh = false;
@@ -361,11 +395,30 @@ __device__ __forceinline__ void gather_node(const RefineArgs &A, const RefShared
         }
         if (lane == 0) ctl->n_new[p] = count;
     }
+    PA_GTICK(5);  // visited bytes
     gather_sync();
+    PA_GTICK(2);
     const int n_new = ctl->n_new[p];
-    // three rows per warp and trip: two through registers, one staged by cp.async
     float *stage = S.stage + (gw + 1) * d;
     const int n_gw = static_cast<int>(blockDim.x >> 5) - 1;  // gather warps
+    if (d > 384) {
+        // two rows per warp and trip, each in one round trip: one through registers,
+        // one staged by cp.async
+        for (int j = gw; j < n_new; j += 2 * n_gw) {
+            const int j1 = j + n_gw;
+            if (j1 < n_new) row_to_stage(stage, A.storage + static_cast<int64_t>(nb_id[j1]) * d, d, 0, lane);
+            const float r0 = one_row(A.storage + static_cast<int64_t>(nb_id[j]) * d, S.q, d, 0, lane);
+            float r1 = 0.0f;
+            if (j1 < n_new) r1 = staged_row(stage, S.q, d, 0, lane);
+            if (lane == 0) {
+                nb_d[j] = r0;
+                if (j1 < n_new) nb_d[j1] = r1;
+            }
+        }
+        PA_GTICK(3);  // vector rows
+        return;
+    }
+    // short rows, three per warp and trip: two through registers, one staged
     for (int j = gw; j < n_new; j += 3 * n_gw) {
         const int j1 = j + n_gw, j2 = j + 2 * n_gw;
         const int v0 = nb_id[j], v1 = j1 < n_new ? nb_id[j1] : v0;
@@ -400,21 +453,37 @@ __device__ __forceinline__ void search_stage(const RefineArgs &A, const RefShare
     if (from < d) {
         float *stage = S.stage + w * d;
         const int n_w = static_cast<int>(blockDim.x >> 5);
-        for (int i = w; i < n_seed; i += 3 * n_w) {
-            const int i1 = i + n_w, i2 = i + 2 * n_w;
-            const int id0 = S.c_id[i], id1 = i1 < n_seed ? S.c_id[i1] : -1;
-            const int id2 = i2 < n_seed ? S.c_id[i2] : -1;
-            if (id0 < 0 && id1 < 0 && id2 < 0) continue;  // warp-uniform
-            if (id2 >= 0) row_to_stage(stage, A.storage + static_cast<int64_t>(id2) * d, d, from, lane);
-            float r0, r1;
-            two_rows(A.storage + static_cast<int64_t>(max(id0, 0)) * d,
-                     A.storage + static_cast<int64_t>(max(id1, 0)) * d, S.q, d, from, lane, r0, r1);
-            float r2 = 0.0f;
-            if (id2 >= 0) r2 = staged_row(stage, S.q, d, from, lane);
-            if (lane == 0) {
-                if (id0 >= 0) S.c_d[i] = __fadd_rn(S.c_d[i], r0);
-                if (id1 >= 0) S.c_d[i1] = __fadd_rn(S.c_d[i1], r1);
-                if (id2 >= 0) S.c_d[i2] = __fadd_rn(S.c_d[i2], r2);
+        if (d - from > 384) {  // long rows: one round trip each, two rows per warp and trip
+            for (int i = w; i < n_seed; i += 2 * n_w) {
+                const int i1 = i + n_w;
+                const int id0 = S.c_id[i], id1 = i1 < n_seed ? S.c_id[i1] : -1;
+                if (id0 < 0 && id1 < 0) continue;  // warp-uniform
+                if (id1 >= 0) row_to_stage(stage, A.storage + static_cast<int64_t>(id1) * d, d, from, lane);
+                float r0 = 0.0f, r1 = 0.0f;
+                if (id0 >= 0) r0 = one_row(A.storage + static_cast<int64_t>(id0) * d, S.q, d, from, lane);
+                if (id1 >= 0) r1 = staged_row(stage, S.q, d, from, lane);
+                if (lane == 0) {
+                    if (id0 >= 0) S.c_d[i] = __fadd_rn(S.c_d[i], r0);
+                    if (id1 >= 0) S.c_d[i1] = __fadd_rn(S.c_d[i1], r1);
+                }
+            }
+        } else {
+            for (int i = w; i < n_seed; i += 3 * n_w) {
+                const int i1 = i + n_w, i2 = i + 2 * n_w;
+                const int id0 = S.c_id[i], id1 = i1 < n_seed ? S.c_id[i1] : -1;
+                const int id2 = i2 < n_seed ? S.c_id[i2] : -1;
+                if (id0 < 0 && id1 < 0 && id2 < 0) continue;  // warp-uniform
+                if (id2 >= 0) row_to_stage(stage, A.storage + static_cast<int64_t>(id2) * d, d, from, lane);
+                float r0, r1;
+                two_rows(A.storage + static_cast<int64_t>(max(id0, 0)) * d,
+                         A.storage + static_cast<int64_t>(max(id1, 0)) * d, S.q, d, from, lane, r0, r1);
+                float r2 = 0.0f;
+                if (id2 >= 0) r2 = staged_row(stage, S.q, d, from, lane);
+                if (lane == 0) {
+                    if (id0 >= 0) S.c_d[i] = __fadd_rn(S.c_d[i], r0);
+                    if (id1 >= 0) S.c_d[i1] = __fadd_rn(S.c_d[i1], r1);
+                    if (id2 >= 0) S.c_d[i2] = __fadd_rn(S.c_d[i2], r2);
+                }
             }
         }
     }
@@ -455,10 +524,11 @@ __device__ __forceinline__ void search_stage(const RefineArgs &A, const RefShare
         const int p = step & 1;
         __syncthreads();
         PA_TICK(4);
+        PA_GTICK(6);  // waiting for the heap warp's pop
         const int u = ctl->pop_u[p];
         if (u < 0) break;
         if (u != ctl->guess[p]) {  // CTA-uniform: nothing, or something else, was prepared
-            if (w > 0) gather_node(A, S, G, vis, marker, ctl, u, p, w - 1, lane);
+            if (w > 0) gather_node(A, S, G, vis, marker, ctl, u, p, w - 1, lane, prof, prof_t);
             __syncthreads();
         }
         PA_TICK(3);
@@ -474,7 +544,11 @@ __device__ __forceinline__ void search_stage(const RefineArgs &A, const RefShare
                 if (dist >= -S.buf[1].k) continue;
                 warp_pushpop(S.buf, H, -dist, nb_id[j], lane, WL);
                 warp_replace(S.open, 2 * H, dist, nb_id[j], lane, WL);
+#if PA_REFINE_PROFILE
+                if (PA_REFINE_PROFILE == 1 && threadIdx.x == 0) prof[7] += 1;
+#endif
             }
+            PA_TICK(5);
             if (step + 1 < max_iter) {
                 const HeapEntry nx = warp_pop(S.open, 2 * H, lane, WL);
                 const bool stop = nx.v < 0 || nx.k >= -S.buf[1].k;
@@ -484,6 +558,7 @@ __device__ __forceinline__ void search_stage(const RefineArgs &A, const RefShare
                     ctl->root_v[p ^ 1] = S.open[1].v;
                 }
             }
+            PA_TICK(2);
         } else if (speculate && step + 1 < max_iter) {
             // the node the next pop returns unless it ends the search: the first
             // new neighbour with the smallest distance if that is below the root
@@ -504,7 +579,7 @@ __device__ __forceinline__ void search_stage(const RefineArgs &A, const RefShare
             }
             const int guess = best < ctl->root_k[p] ? S.nb_id[p * kMaxDegree + at] : ctl->root_v[p];
             if (tid == 32) ctl->guess[p ^ 1] = guess;
-            if (guess >= 0) gather_node(A, S, G, vis, marker, ctl, guess, p ^ 1, w - 1, lane);
+            if (guess >= 0) gather_node(A, S, G, vis, marker, ctl, guess, p ^ 1, w - 1, lane, prof, prof_t);
         }
         PA_TICK(5);
     }
@@ -578,7 +653,10 @@ __global__ void __launch_bounds__(kRefThreads, PA_REFINE_MIN_CTAS) refine_kernel
         __syncthreads();
         int st[4] = {0, 0, 0, 0};
         int prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        long long prof_t = clock64();
+        long long prof_t = 0;
+#if PA_REFINE_PROFILE
+        prof_t = pinned_clock();
+#endif
         // stage 2 (traverse_cpu.cpp:317-326): sub-graph, REFINE_STEP expansions
         search_stage(A, S, A.sub, vis, static_cast<uint8_t>(marker), A.n_cand, A.d_p,
                      min(2, 2 * A.ef), A.n_cand, false, ctl, st[0], st[1], prof, prof_t);
@@ -592,10 +670,14 @@ __global__ void __launch_bounds__(kRefThreads, PA_REFINE_MIN_CTAS) refine_kernel
             A.out_I[b * k_out + i] = S.c_id[i];
             A.out_D[b * k_out + i] = S.c_d[i];
         }
+#if PA_REFINE_PROFILE
+        if (A.stats != nullptr && tid == 32)
+            for (int i = 0; i < 8; ++i) A.stats[b * 24 + 12 + i] = prof[i];
+#endif
         if (A.stats != nullptr && tid == 0) {
 #if PA_REFINE_PROFILE
-            for (int i = 0; i < 4; ++i) A.stats[b * 16 + i] = st[i];
-            for (int i = 0; i < 8; ++i) A.stats[b * 16 + 4 + i] = prof[i];
+            for (int i = 0; i < 4; ++i) A.stats[b * 24 + i] = st[i];
+            for (int i = 0; i < 8; ++i) A.stats[b * 24 + 4 + i] = prof[i];
 #else
 #pragma unroll
             for (int i = 0; i < 4; ++i) A.stats[b * 4 + i] = st[i];
