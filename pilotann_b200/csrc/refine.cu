@@ -350,6 +350,7 @@ struct RefCtl {
     int root_v[2];
     int guess[2];       // node the gather warps prepared expansion i for
     int n_new[2];       // unvisited neighbours found for expansion i
+    int tie;            // sorted_output met equal distances: pop the heap instead
     int marker;
 };
 
@@ -436,6 +437,59 @@ __device__ __forceinline__ void gather_node(const RefineArgs &A, const RefShared
     }
 }
 
+// The last step of traverse_cpu_kernel (traverse_cpu.cpp:149-162) pops the result
+// heap H times: the H - k_out worst entries are dropped, the others come out worst
+// first and are stored ascending.  Popping a heap whose keys are pairwise different
+// yields them in sorted order whatever the layout, so the CTA sorts a copy of the
+// heap (bitonic network in the open heap's memory, which is dead by now) and stores
+// the n_real best.  Two equal distances (other than between pads) make the order
+// depend on the layout: nothing is written then and the caller pops.  Returns true
+// (CTA-uniform) if the output has been written.
+__device__ __forceinline__ bool sorted_output(const RefShared &S, int H, int n_real, int k_out,
+                                              RefCtl *ctl) {
+    const int tid = threadIdx.x, n_thr = blockDim.x;
+    HeapEntry *a = S.open;  // {distance, id}, 2H + 2 entries available
+    int P = 1;
+    while (P < H) P <<= 1;  // P <= 2H - 1
+    if (tid == 0) ctl->tie = 0;
+    for (int i = tid; i < P; i += n_thr) {
+        HeapEntry e = HeapEntry{CUDART_INF_F, -1};
+        if (i < H) {
+            e = S.buf[1 + i];
+            e.k = -e.k;
+        }
+        a[i] = e;
+    }
+    __syncthreads();
+    for (int size = 2; size <= P; size <<= 1) {
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            for (int t = tid; t < (P >> 1); t += n_thr) {
+                const int lo = 2 * t - (t & (stride - 1));  // index with bit `stride` clear
+                const int hi = lo + stride;
+                const bool up = (lo & size) == 0;
+                const HeapEntry x = a[lo], y = a[hi];
+                if ((x.k > y.k) == up) {
+                    a[lo] = y;
+                    a[hi] = x;
+                }
+            }
+            __syncthreads();
+        }
+    }
+    bool tie = false;
+    for (int i = tid; i + 1 < H; i += n_thr)
+        if (a[i].k == a[i + 1].k && (a[i].v >= 0 || a[i + 1].v >= 0)) tie = true;
+    if (tie) ctl->tie = 1;
+    __syncthreads();
+    if (ctl->tie != 0) return false;
+    for (int r = tid; r < n_real; r += n_thr) {
+        const HeapEntry e = a[r];
+        S.c_id[k_out - n_real + r] = e.v;
+        S.c_d[k_out - n_real + r] = e.k;
+    }
+    return true;
+}
+
 // One call of upstream's traverse_cpu_kernel: seeds in c_id / c_d (n_seed of
 // them), the result (k_out entries, ascending behind (-1, -inf) pads) back into
 // c_id / c_d.  `from` < d: the seeds' distances are first completed over dims
@@ -487,6 +541,7 @@ __device__ __forceinline__ void search_stage(const RefineArgs &A, const RefShare
             }
         }
     }
+    PA_GTICK(4);  // residual distances of the seeds
     // :65-68
     for (int i = tid; i < H + 2; i += blockDim.x) S.buf[i] = HeapEntry{-CUDART_INF_F, -1};
     for (int i = tid; i < 2 * H + 2; i += blockDim.x) S.open[i] = HeapEntry{CUDART_INF_F, -1};
@@ -524,7 +579,7 @@ __device__ __forceinline__ void search_stage(const RefineArgs &A, const RefShare
         const int p = step & 1;
         __syncthreads();
         PA_TICK(4);
-        PA_GTICK(6);  // waiting for the heap warp's pop
+        if (step == 0) { PA_GTICK(7); } else { PA_GTICK(6); }  // waiting for the heap warp: seed inserts / a pop
         const int u = ctl->pop_u[p];
         if (u < 0) break;
         if (u != ctl->guess[p]) {  // CTA-uniform: nothing, or something else, was prepared
@@ -591,10 +646,10 @@ __device__ __forceinline__ void search_stage(const RefineArgs &A, const RefShare
             const int id = S.c_id[i];
             if (id >= 0) warp_pushpop(S.buf, H, -S.c_d[i], id, lane, WL);
         }
-        for (int i = k_out; i < H; ++i) warp_pop(S.buf, H, lane, WL);
     }
     __syncthreads();  // every reader of the seeds is done
-    if (w == 0) {
+    if (!sorted_output(S, H, n_real, k_out, ctl) && w == 0) {
+        for (int i = k_out; i < H; ++i) warp_pop(S.buf, H, lane, WL);
         for (int i = 0; i < n_real; ++i) {
             const HeapEntry e = warp_pop(S.buf, H, lane, WL);
             if (lane == 0) {
@@ -610,6 +665,7 @@ __device__ __forceinline__ void search_stage(const RefineArgs &A, const RefShare
     }
     __syncthreads();
     PA_TICK(6);
+    PA_GTICK(8);  // merge and output (the heap warp alone)
 }
 
 __global__ void __launch_bounds__(kRefThreads, PA_REFINE_MIN_CTAS) refine_kernel(RefineArgs A) {
@@ -652,7 +708,7 @@ __global__ void __launch_bounds__(kRefThreads, PA_REFINE_MIN_CTAS) refine_kernel
         }
         __syncthreads();
         int st[4] = {0, 0, 0, 0};
-        int prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        int prof[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
         long long prof_t = 0;
 #if PA_REFINE_PROFILE
         prof_t = pinned_clock();
@@ -672,7 +728,7 @@ __global__ void __launch_bounds__(kRefThreads, PA_REFINE_MIN_CTAS) refine_kernel
         }
 #if PA_REFINE_PROFILE
         if (A.stats != nullptr && tid == 32)
-            for (int i = 0; i < 8; ++i) A.stats[b * 24 + 12 + i] = prof[i];
+            for (int i = 0; i < 12; ++i) A.stats[b * 24 + 12 + i] = prof[i];
 #endif
         if (A.stats != nullptr && tid == 0) {
 #if PA_REFINE_PROFILE
