@@ -350,7 +350,8 @@ struct RefCtl {
     int root_v[2];
     int guess[2];       // node the gather warps prepared expansion i for
     int n_new[2];       // unvisited neighbours found for expansion i
-    int tie;            // sorted_output met equal distances: pop the heap instead
+    int tie;            // select_sort_output gave up: run upstream's sequence
+    int n_taken, n_equal;
     int marker;
 };
 
@@ -437,30 +438,98 @@ __device__ __forceinline__ void gather_node(const RefineArgs &A, const RefShared
     }
 }
 
-// The last step of traverse_cpu_kernel (traverse_cpu.cpp:149-162) pops the result
-// heap H times: the H - k_out worst entries are dropped, the others come out worst
-// first and are stored ascending.  Popping a heap whose keys are pairwise different
-// yields them in sorted order whatever the layout, so the CTA sorts a copy of the
-// heap (bitonic network in the open heap's memory, which is dead by now) and stores
-// the n_real best.  Two equal distances (other than between pads) make the order
-// depend on the layout: nothing is written then and the caller pops.  Returns true
-// (CTA-uniform) if the output has been written.
-__device__ __forceinline__ bool sorted_output(const RefShared &S, int H, int n_real, int k_out,
-                                              RefCtl *ctl) {
+// The end of traverse_cpu_kernel (traverse_cpu.cpp:139-162) without heap operations.
+// Upstream pushes every seed into the result heap (heap_pushpop keeps the H
+// smallest distances; one equal to the current worst stays out), pops the H - k_out
+// worst entries and stores the others worst first, i.e. ascending.  When the
+// distances that matter are pairwise different, that is the n_real smallest of
+// (result heap + seeds) in ascending order, whatever the heaps looked like on the
+// way.  So: (1) a radix select over the float bit patterns (non-negative floats
+// order like their bits; eight 4-bit passes with 16 shared counters) finds the H-th
+// smallest distance T, (2) the entries below T and as many of those equal to T as
+// still fit are gathered into the open heap's memory (dead by now), (3) a bitonic
+// network sorts them, (4) the first n_real are stored.  More entries equal to T than
+// fit, two equal distances among the chosen (pads of the result heap, (-1, +inf),
+// excepted: they are interchangeable), or a distance that is negative or NaN make
+// the outcome depend on upstream's exact sequence: nothing is written then and the
+// caller runs that sequence.  Returns true (CTA-uniform) if the output is written.
+__device__ __forceinline__ bool select_sort_output(const RefShared &S, int H, int n_seed,
+                                                   int n_real, int k_out, RefCtl *ctl) {
     const int tid = threadIdx.x, n_thr = blockDim.x;
-    HeapEntry *a = S.open;  // {distance, id}, 2H + 2 entries available
-    int P = 1;
-    while (P < H) P <<= 1;  // P <= 2H - 1
-    if (tid == 0) ctl->tie = 0;
-    for (int i = tid; i < P; i += n_thr) {
-        HeapEntry e = HeapEntry{CUDART_INF_F, -1};
-        if (i < H) {
-            e = S.buf[1 + i];
-            e.k = -e.k;
+    const int N = H + n_seed;
+    int *bins = reinterpret_cast<int *>(S.open);  // 16 counters, then the gathered entries
+    HeapEntry *a = S.open;
+    if (tid == 0) {
+        ctl->tie = 0;
+        ctl->n_taken = 0;
+        ctl->n_equal = 0;
+    }
+    // (1) the H-th smallest key
+    unsigned prefix = 0, mask = 0;
+    int want = H, at_T = 0;
+    bool bad = false;
+    for (int shift = 28; shift >= 0; shift -= 4) {
+        __syncthreads();
+        if (tid < 16) bins[tid] = 0;
+        __syncthreads();
+        for (int x = tid; x < N; x += n_thr) {
+            float dx;
+            if (x < H) {
+                dx = -S.buf[1 + x].k;
+            } else {
+                if (S.c_id[x - H] < 0) continue;
+                dx = S.c_d[x - H];
+            }
+            if (!(dx >= 0.0f)) bad = true;
+            const unsigned key = __float_as_uint(dx);
+            if ((key & mask) == prefix) atomicAdd(&bins[(key >> shift) & 15u], 1);
         }
-        a[i] = e;
+        __syncthreads();
+        int before = 0, digit = 15;
+        bool found = false;
+#pragma unroll
+        for (int b = 0; b < 16; ++b) {  // every thread, same result
+            const int c = bins[b];
+            if (!found) {
+                if (before + c < want) {
+                    before += c;
+                } else {
+                    digit = b;
+                    found = true;
+                }
+            }
+        }
+        want -= before;
+        at_T = bins[digit];
+        prefix |= static_cast<unsigned>(digit) << shift;
+        mask |= 15u << shift;
+    }
+    const unsigned T = prefix;  // `want` of the at_T entries equal to T are needed
+    if (at_T > want && T != __float_as_uint(CUDART_INF_F)) bad = true;
+    if (bad) ctl->tie = 1;
+    __syncthreads();
+    if (ctl->tie != 0) return false;
+    // (2) gather
+    int P = 1;
+    while (P < H) P <<= 1;  // P <= 2H - 1 entries fit
+    for (int i = H + tid; i < P; i += n_thr) a[i] = HeapEntry{CUDART_INF_F, -1};
+    for (int x = tid; x < N; x += n_thr) {
+        HeapEntry e;
+        if (x < H) {
+            e = S.buf[1 + x];
+            e.k = -e.k;
+        } else {
+            e.v = S.c_id[x - H];
+            if (e.v < 0) continue;
+            e.k = S.c_d[x - H];
+        }
+        const unsigned key = __float_as_uint(e.k);
+        bool take = key < T;
+        if (key == T) take = atomicAdd(&ctl->n_equal, 1) < want;
+        if (take) a[atomicAdd(&ctl->n_taken, 1)] = e;
     }
     __syncthreads();
+    // (3) sort ascending
     for (int size = 2; size <= P; size <<= 1) {
         for (int stride = size >> 1; stride > 0; stride >>= 1) {
             for (int t = tid; t < (P >> 1); t += n_thr) {
@@ -482,6 +551,7 @@ __device__ __forceinline__ bool sorted_output(const RefShared &S, int H, int n_r
     if (tie) ctl->tie = 1;
     __syncthreads();
     if (ctl->tie != 0) return false;
+    // (4)
     for (int r = tid; r < n_real; r += n_thr) {
         const HeapEntry e = a[r];
         S.c_id[k_out - n_real + r] = e.v;
@@ -641,20 +711,22 @@ __device__ __forceinline__ void search_stage(const RefineArgs &A, const RefShare
     // :139-162: the seeds join the result heap; all but k_out are dropped; what is
     // left comes out worst first and is stored ascending
     const int n_real = min(k_out, H);
-    if (w == 0) {
-        for (int i = 0; i < n_seed; ++i) {
-            const int id = S.c_id[i];
-            if (id >= 0) warp_pushpop(S.buf, H, -S.c_d[i], id, lane, WL);
+    if (!select_sort_output(S, H, n_seed, n_real, k_out, ctl)) {  // CTA-uniform
+        if (w == 0) {
+            for (int i = 0; i < n_seed; ++i) {
+                const int id = S.c_id[i];
+                if (id >= 0) warp_pushpop(S.buf, H, -S.c_d[i], id, lane, WL);
+            }
+            for (int i = k_out; i < H; ++i) warp_pop(S.buf, H, lane, WL);
         }
-    }
-    __syncthreads();  // every reader of the seeds is done
-    if (!sorted_output(S, H, n_real, k_out, ctl) && w == 0) {
-        for (int i = k_out; i < H; ++i) warp_pop(S.buf, H, lane, WL);
-        for (int i = 0; i < n_real; ++i) {
-            const HeapEntry e = warp_pop(S.buf, H, lane, WL);
-            if (lane == 0) {
-                S.c_id[k_out - i - 1] = e.v;
-                S.c_d[k_out - i - 1] = -e.k;
+        __syncthreads();  // the seeds have been read: their slots may be overwritten
+        if (w == 0) {
+            for (int i = 0; i < n_real; ++i) {
+                const HeapEntry e = warp_pop(S.buf, H, lane, WL);
+                if (lane == 0) {
+                    S.c_id[k_out - i - 1] = e.v;
+                    S.c_d[k_out - i - 1] = -e.k;
+                }
             }
         }
     }
