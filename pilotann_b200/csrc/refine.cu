@@ -345,6 +345,8 @@ struct RefShared {
 
 // What the heap warp publishes after a pop, and the gather side's guess.
 struct RefCtl {
+    unsigned long long m1, m2;  // brief_search: the two smallest seeds, key bits << 32 | index
+    int c1, c2;                 //               other seeds with the same distances
     int pop_u[2];       // node popped for expansion i (slot i & 1), -1: the search ends
     float root_k[2];    // open heap's root right after that pop
     int root_v[2];
@@ -560,6 +562,139 @@ __device__ __forceinline__ bool select_sort_output(const RefShared &S, int H, in
     return true;
 }
 
+// A search of exactly two expansions (the sub-graph stage: REFINE_STEP = 2,
+// traverse_cpu.cpp:317-326) without the open heap.  heap_replace only ever drops or
+// evicts an entry that is no smaller than the leaf at the end of a larger-child
+// walk, and at least four entries of a heap of 32 or more are no larger than that
+// leaf (the root, its larger child and that child's sibling, the next node of the
+// walk) -- so the two smallest keys ever offered are in the heap when they are
+// popped, and with pairwise different keys the two pops are simply: the smallest
+// seed, then the smaller of the second-smallest seed and the best neighbour
+// admitted during the first expansion.  The result heap is kept exactly as
+// upstream keeps it (its worst entry decides admissions and the stop test).
+// Whenever the keys that matter are not pairwise different the layout of the open
+// heap decides: with equal smallest seeds nothing is done and false is returned (the
+// caller runs upstream's sequence); a tie met at the second pop is settled by
+// building the open heap after all, in upstream's order, and popping it.
+// Called by all threads after the seeds are marked; returns CTA-uniformly.
+__device__ __forceinline__ bool brief_search(const RefineArgs &A, const RefShared &S,
+                                             const RefGraph &G, uint8_t *vis, uint8_t marker,
+                                             int n_seed, RefCtl *ctl, const WalkLane &WL,
+                                             int &n_expand, int &n_eval, int *prof,
+                                             long long &prof_t) {
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, n_thr = blockDim.x;
+    const int H = A.H;
+    constexpr unsigned long long kNone = ~0ull;
+    if (tid == 0) {
+        ctl->m1 = ctl->m2 = kNone;
+        ctl->c1 = ctl->c2 = 0;
+        ctl->tie = 0;
+    }
+    __syncthreads();
+    bool bad = false;
+    for (int i = tid; i < n_seed; i += n_thr) {
+        if (S.c_id[i] < 0) continue;
+        const float dist = S.c_d[i];
+        if (!(dist >= 0.0f && dist < CUDART_INF_F)) bad = true;
+        atomicMin(&ctl->m1, (static_cast<unsigned long long>(__float_as_uint(dist)) << 32) | i);
+    }
+    if (bad) ctl->tie = 1;
+    __syncthreads();
+    const unsigned long long m1 = ctl->m1;
+    const int i1 = static_cast<int>(m1 & 0xffffffffu);
+    for (int i = tid; i < n_seed; i += n_thr) {
+        if (S.c_id[i] < 0 || i == i1) continue;
+        const unsigned key = __float_as_uint(S.c_d[i]);
+        if (key == static_cast<unsigned>(m1 >> 32)) atomicAdd(&ctl->c1, 1);
+        atomicMin(&ctl->m2, (static_cast<unsigned long long>(key) << 32) | i);
+    }
+    __syncthreads();
+    if (ctl->tie != 0 || ctl->c1 != 0) return false;  // nothing has been changed
+    const unsigned long long m2 = ctl->m2;
+    const int i2 = static_cast<int>(m2 & 0xffffffffu);
+    for (int i = tid; i < n_seed; i += n_thr) {
+        if (S.c_id[i] < 0 || i == i1 || i == i2) continue;
+        if (__float_as_uint(S.c_d[i]) == static_cast<unsigned>(m2 >> 32)) atomicAdd(&ctl->c2, 1);
+    }
+    __syncthreads();
+    if (m1 == kNone) return true;  // no seed at all: the first pop ends the search
+    // first pop: the smallest seed; the result heap is empty, the stop test passes
+    const int u1 = S.c_id[i1];
+    if (w > 0) gather_node(A, S, G, vis, marker, ctl, u1, 0, w - 1, lane, prof, prof_t);
+    __syncthreads();
+    if (w == 0) {
+        const int n_new = ctl->n_new[0];
+        ++n_expand;
+        n_eval += n_new;
+        unsigned long long admitted = 0;
+        float best = CUDART_INF_F;
+        int best_j = -1;
+        bool best_twice = false;
+        for (int j = 0; j < n_new; ++j) {  // heap_update (:23-39) without the open heap
+            const float dist = S.nb_d[j];
+            if (dist >= -S.buf[1].k) continue;
+            warp_pushpop(S.buf, H, -dist, S.nb_id[j], lane, WL);
+            admitted |= 1ull << j;
+            if (dist < best) {
+                best = dist;
+                best_j = j;
+                best_twice = false;
+            } else if (dist == best) {
+                best_twice = true;
+            }
+        }
+        // second pop
+        const bool seed_left = m2 != kNone;
+        const float seed_k = seed_left ? S.c_d[i2] : CUDART_INF_F;
+        int u2 = -1;
+        float k2 = CUDART_INF_F;
+        bool unsure = false;
+        if (best_j >= 0 && (!seed_left || best < seed_k)) {
+            u2 = S.nb_id[best_j];
+            k2 = best;
+            unsure = best_twice;
+        } else if (seed_left && (best_j < 0 || seed_k < best)) {
+            u2 = S.c_id[i2];
+            k2 = seed_k;
+            unsure = ctl->c2 != 0;
+        } else if (seed_left) {  // equal
+            unsure = true;
+        }
+        if (unsure) {  // upstream's sequence on the open heap
+            for (int i = 0; i < n_seed; ++i) {
+                const int id = S.c_id[i];
+                if (id >= 0) warp_replace(S.open, 2 * H, S.c_d[i], id, lane, WL);
+            }
+            warp_pop(S.open, 2 * H, lane, WL);
+            for (int j = 0; j < n_new; ++j)
+                if ((admitted >> j) & 1ull) warp_replace(S.open, 2 * H, S.nb_d[j], S.nb_id[j], lane, WL);
+            const HeapEntry nx = warp_pop(S.open, 2 * H, lane, WL);
+            u2 = nx.v;
+            k2 = nx.k;
+        }
+        if (u2 >= 0 && k2 >= -S.buf[1].k) u2 = -1;  // :86-90
+        if (lane == 0) ctl->pop_u[1] = u2;
+    }
+    __syncthreads();
+    const int u2 = ctl->pop_u[1];
+    if (u2 < 0) return true;
+    if (w > 0) gather_node(A, S, G, vis, marker, ctl, u2, 1, w - 1, lane, prof, prof_t);
+    __syncthreads();
+    if (w == 0) {
+        const int n_new = ctl->n_new[1];
+        const int32_t *nb_id = S.nb_id + kMaxDegree;
+        const float *nb_d = S.nb_d + kMaxDegree;
+        ++n_expand;
+        n_eval += n_new;
+        for (int j = 0; j < n_new; ++j) {
+            const float dist = nb_d[j];
+            if (dist >= -S.buf[1].k) continue;
+            warp_pushpop(S.buf, H, -dist, nb_id[j], lane, WL);
+        }
+    }
+    return true;
+}
+
 // One call of upstream's traverse_cpu_kernel: seeds in c_id / c_d (n_seed of
 // them), the result (k_out entries, ascending behind (-1, -inf) pads) back into
 // c_id / c_d.  `from` < d: the seeds' distances are first completed over dims
@@ -623,7 +758,9 @@ __device__ __forceinline__ void search_stage(const RefineArgs &A, const RefShare
     __syncthreads();
     PA_TICK(0);
     const WalkLane WL = walk_lane(lane);
-    if (w == 0) {
+    const bool brief = max_iter == 2 && !speculate && 2 * H >= 32 && G.degree <= 64 &&
+                       brief_search(A, S, G, vis, marker, n_seed, ctl, WL, n_expand, n_eval, prof, prof_t);
+    if (!brief && w == 0) {
         for (int i = 0; i < n_seed; ++i) {
             const int id = S.c_id[i];
             if (id >= 0) warp_replace(S.open, 2 * H, S.c_d[i], id, lane, WL);
@@ -634,7 +771,7 @@ __device__ __forceinline__ void search_stage(const RefineArgs &A, const RefShare
     // neighbour buffers.  Per expansion one CTA-wide barrier: behind it the heap
     // warp has popped node i (or ended the search) and -- when speculating --
     // the gather warps have prepared the node they expected.
-    if (w == 0) {
+    if (!brief && w == 0) {
         const HeapEntry u = warp_pop(S.open, 2 * H, lane, WL);
         const bool stop = max_iter <= 0 || u.v < 0 || u.k >= -S.buf[1].k;
         if (lane == 0) {
@@ -645,7 +782,7 @@ __device__ __forceinline__ void search_stage(const RefineArgs &A, const RefShare
         }
     }
     PA_TICK(2);
-    for (int step = 0; step < max_iter; ++step) {
+    for (int step = 0; step < max_iter && !brief; ++step) {
         const int p = step & 1;
         __syncthreads();
         PA_TICK(4);

@@ -307,6 +307,52 @@ def test_three_warp_ctas_for_short_rows(oracle_lib):
     assert torch.equal(s_I, t_I[:200]) and torch.equal(s_D.view(torch.int32), t_D[:200].view(torch.int32))
 
 
+def test_equal_distances_take_upstreams_sequence(oracle_lib):
+    """Vectors on a coarse grid, many of them identical: equal distances everywhere.
+    The shortcuts of the kernel (two-expansion stage without the open heap, seeds
+    merged by selection and sort) give way to upstream's heap sequence wherever two
+    keys that matter are equal -- same bits as the oracle, statistics included."""
+    from pilotann_b200 import extension
+    from helpers import make_problem
+    g = torch.Generator().manual_seed(123)
+    for d, d_p, ef, k, levels, dup in [(64, 32, 24, 10, 2.0, 6), (96, 32, 48, 10, 1.0, 3),
+                                       (200, 64, 16, 5, 4.0, 10), (768, 128, 32, 10, 1.0, 4)]:
+        B = 48
+        p = make_problem(n=3000, d=d, ratio=0.5, batch=B, n_init=32, seed=300 + d)
+        full = torch.round(p["full"] * levels) / levels
+        full[torch.randperm(3000, generator=g)] = full.repeat_interleave(dup, 0)[:3000]
+        full = full.contiguous()
+        q = (torch.round(p["query"] * levels) / levels).contiguous()
+        ids = p["nodelist"][torch.randint(p["nodelist"].numel(), (B, 4 * ef), generator=g)]
+        ids[torch.rand(B, 4 * ef, generator=g) < 0.1] = -1
+        dist = ((q[:, :d_p].unsqueeze(1) - full[ids.clamp_min(0)][:, :, :d_p]) ** 2).sum(-1)
+        dist[ids < 0] = float("inf")
+        dist = dist.contiguous()
+        nbr, row_of = extension.pack_graph(p["indptr"].cuda(), p["indices"].cuda(), p["mapping"].cuda(),
+                                           p["storage"].size(0), 32)
+        full_nbr = extension.pack_fullgraph(p["full_indptr"].cuda(), p["full_indices"].cuda(), 32)
+        pool = extension.VisitedPool(full.size(0), 16)
+        graphs = ([p["indptr"], p["indices"]], [p["full_indptr"], p["full_indices"]])
+        for stages_k in (None, k):
+            st = torch.zeros(B, 4, dtype=torch.int32, device="cuda")
+            t_I, t_D = extension.refine(ids.cuda(), dist.cuda(), q.cuda(), full.cuda(), nbr, row_of,
+                                        full_nbr if stages_k else None, pool, ef, d_p, k=stages_k,
+                                        stats=st)
+            torch.cuda.synchronize()
+            w_bI, w_bD = ids.clone(), dist.clone()
+            w_I, w_D, w_st = oracle_lib.refine_ex(w_bI, w_bD, *graphs, full, q, k, ef, d_p, gpu_order=True,
+                                                  stages=3 if stages_k else 2, with_stats=True)
+            if stages_k is None:
+                w_I, w_D, w_st = w_bI, w_bD, w_st[:, :2]
+                st = st[:, :2]
+            assert torch.equal(t_I.cpu(), w_I), (d, ef, stages_k)
+            assert torch.equal(t_D.cpu().view(torch.int32), w_D.view(torch.int32)), (d, ef, stages_k)
+            assert torch.equal(st.cpu(), w_st), (d, ef, stages_k)
+        # the case is what it claims to be: equal distances among a query's candidates
+        row = dist[0][ids[0] >= 0]
+        assert row.unique().numel() < row.numel()
+
+
 def test_replay_of_upstream_fixtures():
     """Outputs of upstream ``traverse_refine`` recorded by tests/golden/make_golden.py
     (CPU, no GPU involved), replayed through the refinement kernel without the
