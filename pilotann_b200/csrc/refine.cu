@@ -353,6 +353,7 @@ struct RefCtl {
     int guess[2];       // node the gather warps prepared expansion i for
     int n_new[2];       // unvisited neighbours found for expansion i
     int tie;            // select_sort_output gave up: run upstream's sequence
+    int sorted;         // the last select_sort_output wrote its output (strictly ascending)
     int n_taken, n_equal;
     int marker;
 };
@@ -703,7 +704,8 @@ __device__ __forceinline__ bool brief_search(const RefineArgs &A, const RefShare
 __device__ __forceinline__ void search_stage(const RefineArgs &A, const RefShared &S,
                                              const RefGraph &G, uint8_t *vis, uint8_t marker,
                                              int n_seed, int from, int max_iter, int k_out,
-                                             bool speculate, RefCtl *ctl, int &n_expand, int &n_eval, int *prof,
+                                             bool speculate, bool seeds_sorted, RefCtl *ctl,
+                                             int &n_expand, int &n_eval, int *prof,
                                              long long &prof_t) {
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     const int d = A.d, H = A.H;
@@ -761,9 +763,26 @@ __device__ __forceinline__ void search_stage(const RefineArgs &A, const RefShare
     const bool brief = max_iter == 2 && !speculate && 2 * H >= 32 && G.degree <= 64 &&
                        brief_search(A, S, G, vis, marker, n_seed, ctl, WL, n_expand, n_eval, prof, prof_t);
     if (!brief && w == 0) {
-        for (int i = 0; i < n_seed; ++i) {
-            const int id = S.c_id[i];
-            if (id >= 0) warp_replace(S.open, 2 * H, S.c_d[i], id, lane, WL);
+        if (seeds_sorted && ctl->sorted != 0 && n_seed >= H) {
+            // The real seeds are c[n_seed - H ..] in strictly ascending order.  Every
+            // key offered to heap_replace is then larger than all keys in the heap:
+            // it replaces a +inf leaf and climbs to just below a real entry, or meets
+            // a real leaf and is dropped -- which of the two depends on the count of
+            // seeds before it only.  Seed 0 ends at heap index 0, seeds 2t - 1 and 2t
+            // at the two rightmost nodes of level t (2^(t+1) - 3 and 2^(t+1) - 2,
+            // 0-based) while those exist; all later seeds are dropped.  Checked
+            // against heap_replace for every heap size and seed count on the host.
+            const int t = (lane + 1) >> 1;
+            const int pos = lane == 0 ? 0 : (1 << (t + 1)) - 3 + ((lane & 1) ? 0 : 1);
+            const int at = n_seed - H + lane;
+            if (lane < 25 && pos < 2 * H && at < n_seed && S.c_id[at] >= 0)
+                S.open[1 + pos] = HeapEntry{S.c_d[at], S.c_id[at]};
+            __syncwarp();
+        } else {
+            for (int i = 0; i < n_seed; ++i) {
+                const int id = S.c_id[i];
+                if (id >= 0) warp_replace(S.open, 2 * H, S.c_d[i], id, lane, WL);
+            }
         }
     }
     PA_TICK(1);
@@ -848,7 +867,9 @@ __device__ __forceinline__ void search_stage(const RefineArgs &A, const RefShare
     // :139-162: the seeds join the result heap; all but k_out are dropped; what is
     // left comes out worst first and is stored ascending
     const int n_real = min(k_out, H);
-    if (!select_sort_output(S, H, n_seed, n_real, k_out, ctl)) {  // CTA-uniform
+    const bool sorted = select_sort_output(S, H, n_seed, n_real, k_out, ctl);  // CTA-uniform
+    if (tid == 0) ctl->sorted = sorted;  // the output is strictly ascending up to its trailing pads
+    if (!sorted) {
         if (w == 0) {
             for (int i = 0; i < n_seed; ++i) {
                 const int id = S.c_id[i];
@@ -874,7 +895,7 @@ __device__ __forceinline__ void search_stage(const RefineArgs &A, const RefShare
     }
     __syncthreads();
     PA_TICK(6);
-    PA_GTICK(8);  // merge and output (the heap warp alone)
+    PA_GTICK(8);  // merge and output
 }
 
 __global__ void __launch_bounds__(kRefThreads, PA_REFINE_MIN_CTAS) refine_kernel(RefineArgs A) {
@@ -924,11 +945,11 @@ __global__ void __launch_bounds__(kRefThreads, PA_REFINE_MIN_CTAS) refine_kernel
 #endif
         // stage 2 (traverse_cpu.cpp:317-326): sub-graph, REFINE_STEP expansions
         search_stage(A, S, A.sub, vis, static_cast<uint8_t>(marker), A.n_cand, A.d_p,
-                     min(2, 2 * A.ef), A.n_cand, false, ctl, st[0], st[1], prof, prof_t);
+                     min(2, 2 * A.ef), A.n_cand, false, false, ctl, st[0], st[1], prof, prof_t);
         int k_out = A.n_cand;
         if (A.stages >= 3) {  // stage 3 (:327-336): full graph, same marker
             search_stage(A, S, A.full, vis, static_cast<uint8_t>(marker), A.n_cand, A.d,
-                         min(1024, 2 * A.ef), A.k, true, ctl, st[2], st[3], prof, prof_t);
+                         min(1024, 2 * A.ef), A.k, true, true, ctl, st[2], st[3], prof, prof_t);
             k_out = A.k;
         }
         for (int i = tid; i < k_out; i += blockDim.x) {
