@@ -52,9 +52,9 @@ OPERATING_EF = {2: 128}
 # it was captured on; None until captured
 NCU_TRAFFIC_PER_QUERY = {2: {
     "traverse": {"bytes_per_query": (1.489819e9 + 7.637e6) / 1024,
-                 "captured_at": "library version 102, 1024 queries, ef 128"},
-    "refine": {"bytes_per_query": (11.399857e9 + 0.135339e9) / 1024,
-               "captured_at": "library version 102, 1024 queries, ef 128"}}}
+                 "captured_at": "library version 102 (kernel unchanged in 103), 1024 queries, ef 128"},
+    "refine": {"bytes_per_query": (11.405134e9 + 0.135800e9) / 1024,
+               "captured_at": "library version 103, 1024 queries, ef 128"}}}
 PASSES = 10       # event-timed passes per step; a step's time is their median
 FALLBACK_HBM_GBS = 6650.0
 

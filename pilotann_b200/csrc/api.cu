@@ -28,6 +28,6 @@ void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
 }  // namespace pa
 
-extern "C" int pa_version(void) { return 102; }  // 102: refinement, visited pool, stage modes and slots
+extern "C" int pa_version(void) { return 103; }  // 103: refinement merges / seeds by selection, narrow CTAs
 extern "C" const char *pa_last_error(void) { return pa::g_error; }
 extern "C" int64_t pa_launch_count(void) { return pa::g_launches.load(std::memory_order_relaxed); }
