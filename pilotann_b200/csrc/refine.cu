@@ -122,6 +122,7 @@ struct RefineArgs {
     float *out_D;
     uint8_t *marks;         // visited pool: slot s at marks + s * slot_stride
     int32_t *epoch;         // [slots] last marker used by the slot
+    unsigned *claim;        // queries handed out beyond each CTA's first, this launch
     int64_t slot_stride;
     int slot_begin;
     int32_t *stats;         // nullptr or [batch, 4]
@@ -353,6 +354,7 @@ struct RefCtl {
     int guess[2];       // node the gather warps prepared expansion i for
     int n_new[2];       // unvisited neighbours found for expansion i
     int tie;            // select_sort_output gave up: run upstream's sequence
+    unsigned next;      // the query claimed for the CTA's next round
     int sorted;         // the last select_sort_output wrote its output (strictly ascending)
     int n_taken, n_equal;
     int marker;
@@ -915,7 +917,9 @@ __global__ void __launch_bounds__(kRefThreads, PA_REFINE_MIN_CTAS) refine_kernel
     const int slot = A.slot_begin + blockIdx.x;
     uint8_t *vis = A.marks + static_cast<int64_t>(slot) * A.slot_stride;
 
-    for (int64_t b = blockIdx.x; b < A.batch; b += gridDim.x) {
+    // CTA i starts on query i; whoever finishes claims the next unclaimed query (queries
+    // differ several-fold in length, and a launch is over when its last CTA is)
+    for (int64_t b = blockIdx.x; b < A.batch;) {
         // next marker of this slot; the array is wiped when the markers run out
         // (bitmask.hpp:17-36 does the same on wrap-around)
         if (tid == 0) ctl->marker = A.epoch[slot] + 1;
@@ -969,7 +973,9 @@ __global__ void __launch_bounds__(kRefThreads, PA_REFINE_MIN_CTAS) refine_kernel
             for (int i = 0; i < 4; ++i) A.stats[b * 4 + i] = st[i];
 #endif
         }
+        if (tid == 0) ctl->next = atomicAdd(A.claim, 1u);
         __syncthreads();
+        b = static_cast<int64_t>(gridDim.x) + ctl->next;
     }
 }
 
@@ -1121,10 +1127,12 @@ int refine_enqueue(int64_t *out_I, float *out_D, const int64_t *cand_I, const fl
     PA_REQUIRE(pool_nodes >= n_nodes, "the visited pool was created for fewer nodes");
     PA_REQUIRE(slot_begin >= 0 && slot_count > 0 && slot_begin + slot_count <= n_slots,
                "slot range outside the visited pool");
-    const RefineArgs A = refine_args(out_I, out_D, cand_I, cand_D, query, ldq, storage_full,
-                                     packed_nbr, row_of, n_neighbors, full_nbr, full_degree, batch,
-                                     n_nodes, d_model, d_principle, n_cand, ef_search, k, stages,
-                                     marks, epoch, slot_stride, slot_begin, stats);
+    RefineArgs A = refine_args(out_I, out_D, cand_I, cand_D, query, ldq, storage_full, packed_nbr,
+                               row_of, n_neighbors, full_nbr, full_degree, batch, n_nodes, d_model,
+                               d_principle, n_cand, ef_search, k, stages, marks, epoch, slot_stride,
+                               slot_begin, stats);
+    A.claim = reinterpret_cast<unsigned *>(epoch + n_slots + slot_begin);
+    PA_CUDA_TRY(cudaMemsetAsync(A.claim, 0, sizeof(unsigned), stream));
     return refine_launch(A, slot_count, stream);
 }
 

@@ -10,7 +10,9 @@
 // mutex-guarded queue -- bumps the slot's marker once per query (1 .. 254) and
 // wipes the slot's array when the markers run out, as Bitmask::advance does on
 // wrap-around.  A byte equal to the current marker means "visited by this query".
-// Memory: n_slots * round_up(n_nodes, 16) bytes, allocated once.
+// Memory: n_slots * round_up(n_nodes, 16) bytes, allocated once.  Beside the markers the
+// pool keeps one counter per slot: the CTAs of a launch claim the queries beyond their
+// first through the counter of the launch's first slot (cleared before the launch).
 //
 // Launches that may run concurrently (different streams) must use disjoint slot
 // ranges; the stage object gives each of its streams its own range.
@@ -20,7 +22,7 @@
 
 struct pa_visited_pool {
     uint8_t *marks = nullptr;
-    int32_t *epoch = nullptr;
+    int32_t *epoch = nullptr;  // [n_slots] last markers, then [n_slots] claim counters
     int64_t n_nodes = 0, slot_stride = 0;
     int n_slots = 0, device = 0;
 };
@@ -39,7 +41,7 @@ void pool_view(const pa_visited_pool *pool, uint8_t **marks, int32_t **epoch, in
 
 extern "C" int64_t pa_visited_pool_bytes(int64_t n_nodes, int n_slots) {
     if (n_nodes <= 0 || n_slots <= 0) return 0;
-    return pa::slot_stride_for(n_nodes) * n_slots + static_cast<int64_t>(sizeof(int32_t)) * n_slots;
+    return pa::slot_stride_for(n_nodes) * n_slots + 2 * static_cast<int64_t>(sizeof(int32_t)) * n_slots;
 }
 
 extern "C" int pa_visited_pool_create(pa_visited_pool **out, int64_t n_nodes, int n_slots) {
@@ -56,9 +58,9 @@ extern "C" int pa_visited_pool_create(pa_visited_pool **out, int64_t n_nodes, in
     cudaError_t e = cudaGetDevice(&pool->device);
     const size_t bytes = static_cast<size_t>(pool->slot_stride) * n_slots;
     if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&pool->marks), bytes);
-    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&pool->epoch), sizeof(int32_t) * n_slots);
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&pool->epoch), 2 * sizeof(int32_t) * n_slots);
     if (e == cudaSuccess) e = cudaMemset(pool->marks, 0, bytes);
-    if (e == cudaSuccess) e = cudaMemset(pool->epoch, 0, sizeof(int32_t) * n_slots);
+    if (e == cudaSuccess) e = cudaMemset(pool->epoch, 0, 2 * sizeof(int32_t) * n_slots);
     if (e != cudaSuccess) {
         pa_visited_pool_destroy(pool);
         return cuda_fail(e, "visited pool allocation");

@@ -198,7 +198,7 @@ def test_rejections():
     import ctypes
     h = ctypes.c_void_p()
     assert lib.pa_visited_pool_create(ctypes.byref(h), 100, 0) == _C.PA_ERR_ARG
-    assert lib.pa_visited_pool_bytes(1000, 4) == 4 * 1008 + 16
+    assert lib.pa_visited_pool_bytes(1000, 4) == 4 * 1008 + 32
 
 
 def test_large_ef_and_wide_rows(oracle_lib):
