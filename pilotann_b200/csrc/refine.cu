@@ -13,11 +13,15 @@
 //
 // The candidates are consumed where the traversal left them, in HBM; nothing of
 // the handoff crosses PCIe.  One CTA of five warps (three for rows of at most 512
-// bytes) per query, persistent: CTA i
-// owns slot i of the visited-set pool (visited.cu) and walks the batch with
-// stride gridDim.x.  Warp 0 is the heap warp (it runs upstream's heap routines),
-// the other warps gather: adjacency row, visited marks, vector rows,
-// distances.  In the full-graph stage the two sides overlap: the node the next
+// bytes) per query, persistent: CTA i owns slot i of the visited-set pool
+// (visited.cu), starts on query i and claims further queries from a counter.
+// Warp 0 is the heap warp (it runs upstream's heap routines), the other warps
+// gather: adjacency row, visited marks, vector rows, distances.  Three serial
+// pieces of upstream's routine -- pushing the seeds into the open heap of the
+// two-expansion stage, seeding the full-graph stage, merging seeds and result --
+// are computed from their outcome when the keys involved are pairwise different
+// (brief_search, the seeding in search_stage, select_sort_output) and run as
+// upstream wrote them otherwise.  In the full-graph stage the two sides overlap: the node the next
 // pop will return is known as soon as the distances of the current expansion are
 // (it is the better of the open heap's root and the best new neighbour -- a new
 // key below the root always sifts up to the root, equal keys never pass it), so
