@@ -53,7 +53,7 @@ OPERATING_EF = {2: 128}
 NCU_TRAFFIC_PER_QUERY = {2: {
     "traverse": {"bytes_per_query": (1.489819e9 + 7.637e6) / 1024,
                  "captured_at": "library version 102 (kernel unchanged in 103), 1024 queries, ef 128"},
-    "refine": {"bytes_per_query": (11.405134e9 + 0.135800e9) / 1024,
+    "refine": {"bytes_per_query": (11.408724e9 + 0.135678e9) / 1024,
                "captured_at": "library version 103, 1024 queries, ef 128"}}}
 PASSES = 10       # event-timed passes per step; a step's time is their median
 FALLBACK_HBM_GBS = 6650.0
