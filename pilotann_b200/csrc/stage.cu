@@ -360,6 +360,15 @@ extern "C" int pa_stage_attach_refine(pa_stage *st, const pa_refine_index *rx,
         PA_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, st->device));
         slots_per_stream = sms * refine_ctas_per_sm(st->ix.d_model);
         if (slots_per_stream > st->max_batch) slots_per_stream = static_cast<int>(st->max_batch);
+        // a slot is one byte per node: on a very large index a full wave of slots is not
+        // affordable -- keep the pool within a quarter of the free memory (fewer resident
+        // queries then, same results)
+        size_t free_b = 0, total_b = 0;
+        PA_CUDA_TRY(cudaMemGetInfo(&free_b, &total_b));
+        const int64_t per_slot = pa_visited_pool_bytes(st->ix.n_nodes, 1) *
+                                 static_cast<int64_t>(st->streams.size());
+        const int64_t affordable = static_cast<int64_t>(free_b / 4) / (per_slot > 0 ? per_slot : 1);
+        if (slots_per_stream > affordable) slots_per_stream = static_cast<int>(affordable < 32 ? 32 : affordable);
     }
     int rc = pa_visited_pool_create(&st->pool, st->ix.n_nodes,
                                     slots_per_stream * static_cast<int>(st->streams.size()));
