@@ -198,3 +198,51 @@ def test_consumer_hook_validation():
     pilotann_b200.set_refine(None)
     assert pilotann_b200.get_refine() is None
     pilotann_b200.set_refine("gpu")
+
+
+def test_heap_replace_properties_the_refinement_kernel_relies_on(oracle_lib):
+    """Two facts about upstream's heap_replace (extension/inc/heapq.cuh:47-77, restated
+    and pinned above) that let the refinement kernel skip serial heap work:
+    (1) keys offered in strictly ascending order to an empty heap of 2H slots end at
+    positions that depend on their rank only -- key 0 at index 0, keys 2t - 1 and 2t at
+    the two rightmost nodes of level t -- and all later keys are dropped;
+    (2) whatever the order, the two smallest keys offered so far are in the heap."""
+    g = torch.Generator().manual_seed(9)
+
+    def position(rank):
+        if rank == 0:
+            return 0
+        level = (rank + 1) // 2
+        return (1 << (level + 1)) - 3 + (0 if rank % 2 == 1 else 1)
+
+    for H in (16, 32, 48, 64, 96, 128, 192, 256, 384, 512, 1024, 2048):
+        cap = 2 * H
+        for count in (0, 1, 2, 5, 9, 16, H // 2, H):
+            keys = torch.rand(4 * H + 8, generator=g).unique()[:count].sort().values
+            assert keys.numel() == count
+            D = torch.full((cap,), float("inf"))
+            I = torch.full((cap,), -1, dtype=torch.int64)
+            for i in range(count):
+                oracle_lib.heap_replace(D, I, float(keys[i]), i)
+            want_D = torch.full((cap,), float("inf"))
+            want_I = torch.full((cap,), -1, dtype=torch.int64)
+            for rank in range(min(count, 64)):
+                if position(rank) < cap:
+                    want_D[position(rank)] = keys[rank]
+                    want_I[position(rank)] = rank
+            assert torch.equal(I, want_I) and torch.equal(D, want_D), (H, count)
+    for H in (16, 24, 64, 128):
+        cap = 2 * H
+        for trial in range(20):
+            n = int(torch.randint(1, 6 * cap, (1,), generator=g))
+            keys = torch.rand(8 * cap, generator=g).unique()[:n]
+            keys = keys[torch.randperm(keys.numel(), generator=g)]
+            D = torch.full((cap,), float("inf"))
+            I = torch.full((cap,), -1, dtype=torch.int64)
+            for i in range(keys.numel()):
+                oracle_lib.heap_replace(D, I, float(keys[i]), i)
+                two = keys[: i + 1].sort().values[:2]
+                assert all((D == k).any() for k in two), (H, trial, i)
+            # ... and a pop returns the smallest of them
+            k, v = oracle_lib.heap_pop(D, I)
+            assert k == float(keys.min()) and v == int(keys.argmin())
